@@ -1,0 +1,111 @@
+"""One DiT transformer block on the B200 kernels (benchmark configuration 4/5).
+
+adaLN modulation -> INT8 QKV GEMM -> per-head QK RMSNorm + 3-D RoPE -> bf16 flash
+attention -> INT8 out-proj -> gated residual -> adaLN -> SwiGLU FFN (INT8 fc1,
+swiglu-quant, INT8 fc2) -> gated residual, on a token shard [L, C].
+
+The reference project has no source for the block itself (it lives in the host
+application's model file); only its operator set comes from the reference.  The
+glue conventions (LayerNorm without affine, RMSNorm weight per head channel,
+rotary on adjacent pairs with three axis bands, bf16 gate vectors) are this
+package's own.  Twelve kernel launches per block on one GPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .ulysses import UlyssesSP
+
+
+def make_block_params(hidden: int = 3072, heads: int = 24, head_dim: int = 128, ffn: int = 8192,
+                      seed: int = 0, device="cuda") -> dict:
+    """Random-init block: weights ~N(0,0.02) quantised per output channel (symmetric
+    int8, scale = absmax/127, round half even, clamp +-127), biases ~N(0,0.01),
+    modulation vectors ~N(0,0.1), norm weights 1 + N(0,0.02)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    p = {}
+
+    def qweight(name, n, k):
+        w = (torch.randn((n, k), generator=g) * 0.02)
+        scale = (w.abs().amax(-1) / 127.0).clamp(min=1e-30)
+        p["wq_" + name] = (w / scale[:, None]).round().clamp(-127, 127).to(torch.int8).to(device)
+        p["ws_" + name] = scale.float().to(device)
+        p["b_" + name] = (torch.randn((n,), generator=g) * 0.01).to(torch.bfloat16).to(device)
+
+    qweight("qkv", 3 * hidden, hidden)
+    qweight("out", hidden, hidden)
+    qweight("fc1", 2 * ffn, hidden)
+    qweight("fc2", hidden, ffn)
+    for name in ("shift1", "scale1", "gate1", "shift2", "scale2", "gate2"):
+        p[name] = (torch.randn((hidden,), generator=g) * 0.1).to(torch.bfloat16).to(device)
+    for name in ("q_norm_w", "k_norm_w"):
+        p[name] = (1.0 + torch.randn((head_dim,), generator=g) * 0.02).to(torch.bfloat16).to(device)
+    p["heads"], p["head_dim"], p["hidden"], p["ffn"] = heads, head_dim, hidden, ffn
+    return p
+
+
+def rope_tables(positions: torch.Tensor, head_dim: int = 128, axes=(32, 48, 48),
+                theta: float = 10000.0):
+    """cos/sin fp32 [S, head_dim/2] for integer positions [S,3] (t, y, x): the head
+    dimension is split into three axis bands; band a rotates adjacent pairs with
+    frequencies theta^(-2i/band).  Computed in float64 on the host side."""
+    assert sum(axes) == head_dim
+    cos, sin = [], []
+    pos = positions.detach().cpu().double()
+    for a, band in enumerate(axes):
+        half = band // 2
+        inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / band)
+        ang = pos[:, a][:, None] * inv[None, :]
+        cos.append(torch.cos(ang).float())
+        sin.append(torch.sin(ang).float())
+    return torch.cat(cos, -1).contiguous(), torch.cat(sin, -1).contiguous()
+
+
+def grid_positions(tokens: int, height: int = 22, width: int = 38) -> torch.Tensor:
+    """Synthetic (t, y, x) coordinates for a joint token stream of `tokens` rows."""
+    idx = torch.arange(tokens)
+    return torch.stack((idx // (height * width), (idx // width) % height, idx % width), dim=-1)
+
+
+class DiTBlock:
+    def __init__(self, params: dict, sp: UlyssesSP | None = None, head_chunks: int = 1,
+                 overlap: bool = True):
+        self.p = params
+        self.sp = sp
+        self.head_chunks = head_chunks
+        self.overlap = overlap
+        self.heads = params["heads"]
+        self.head_dim = params["head_dim"]
+
+    def _attn(self, q, k, v):
+        return ops.fwd_bhsd(q, k, v, self.head_dim ** -0.5)
+
+    def attention(self, qkv: torch.Tensor) -> torch.Tensor:
+        """qkv [L,3,H,D] (normed + rotated) -> [L, H*D]."""
+        L = qkv.shape[0]
+        if self.sp is None or self.sp.world == 1:
+            q, k, v = (qkv[:, i].transpose(0, 1).unsqueeze(0) for i in range(3))
+            out = self._attn(q, k, v)              # [1,H,L,D] view of [1,L,H,D]
+            return out.transpose(1, 2).reshape(L, self.heads * self.head_dim)
+        o = self.sp.attention_fused(qkv, self._attn, chunks=self.head_chunks, overlap=self.overlap)
+        return o.reshape(L, self.heads * self.head_dim)
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """x bf16 [L, C] (this rank's tokens); cos/sin fp32 [L, 64] for the same rows.
+        Returns a new tensor."""
+        p = self.p
+        L = x.shape[0]
+        x = x.clone()
+        q8, s = ops.layernorm_mod_quant(x, p["scale1"], p["shift1"])
+        qkv = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_qkv"], p["ws_qkv"], p["b_qkv"])
+        qkv = qkv.view(L, 3, self.heads, self.head_dim)
+        ops.qk_norm_rope_(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin)
+        o = self.attention(qkv)
+        a = ops.int8_linear(o, p["wq_out"], p["ws_out"], p["b_out"])
+        ops.gate_residual_(x, a, p["gate1"])
+        q8, s = ops.layernorm_mod_quant(x, p["scale2"], p["shift2"])
+        f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])
+        f = ops.int8_linear(f, p["wq_fc2"], p["ws_fc2"], p["b_fc2"], input_act="swiglu")
+        ops.gate_residual_(x, f, p["gate2"])
+        return x

@@ -1,0 +1,38 @@
+// Internal launch functions behind the C ABI (one per kernel family).  Each
+// assumes validated arguments, enqueues on `stream` and returns a b2_status.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b2 {
+
+int launch_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
+                    cudaStream_t stream);
+int launch_swiglu_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
+                           cudaStream_t stream);
+int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t stream);
+int launch_epilogue(const int32_t* acc, const float* rs, const float* cs, const void* bias,
+                    int bias_kind, void* out, int64_t M, int64_t N, cudaStream_t stream);
+int launch_mod_scale_shift(void* x, const void* scale, const void* shift, int64_t M, int64_t C,
+                           cudaStream_t stream);
+int launch_gate_residual(void* x, const void* y, const void* gate, int64_t M, int64_t C,
+                         cudaStream_t stream);
+int launch_layernorm_mod(const void* x, const void* scale, const void* shift, void* out_bf16,
+                         int8_t* out_q, float* out_scale, int64_t M, int64_t C, float eps,
+                         bool quant, cudaStream_t stream);
+int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* cos_tab,
+                        const float* sin_tab, int64_t S, int H, float eps, cudaStream_t stream);
+// out_i32 != nullptr: plain int32 result.  Otherwise the fused dequant epilogue
+// writes bf16 to out_bf16.
+int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
+                     const float* rs, const float* cs, const void* bias, int bias_kind, int64_t M,
+                     int64_t N, int64_t K, cudaStream_t stream);
+int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
+                     const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
+                     cudaStream_t stream);
+
+// Read and clear the device-side status word of a tensor-core translation unit.
+unsigned int read_clear_status_gemm();
+unsigned int read_clear_status_flash();
+
+}  // namespace b2

@@ -1,0 +1,139 @@
+"""Ulysses sequence parallelism around attention, over torch.distributed.
+
+Tokens are sharded across ranks (uneven splits allowed: the first S mod P ranks
+hold one extra row); attention needs every token, so an all-to-all turns the
+token-sharded [L_r, H, D] tensors into head-sharded [S, H/P, D] ones, attention
+runs on the local heads, and a second all-to-all goes back.  Byte layouts follow
+the reference's in-tree model of its sequence-parallel code
+(benchmarks/bench_sp_head_chunk_overlap.py:83-193 in the reference):
+  sequence_to_heads / heads_to_sequence   :83-118
+  packed QKV head chunk [world, L, c, 3, D] -> [S, c, 3, D]   :140-164
+  chunk i attention overlapped with chunk i+1's all-to-all on a side stream   :179-193
+generalised from 2 ranks to any world size dividing the head count.
+
+Works on the NCCL backend (CUDA tensors, NVLink) and on gloo (CPU tensors; used
+by the layout tests).  Received data always lands in local memory before a kernel
+reads it; no kernel here touches a peer's memory.
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def sequence_splits(seq: int, world: int) -> tuple[int, ...]:
+    base, rem = divmod(seq, world)
+    return tuple(base + (1 if r < rem else 0) for r in range(world))
+
+
+class UlyssesSP:
+    def __init__(self, splits: Sequence[int], heads: int, dim: int = 128, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if len(splits) != self.world:
+            raise RuntimeError(f"need {self.world} sequence splits, got {len(splits)}")
+        if heads % self.world:
+            raise RuntimeError("world size must divide the head count")
+        self.splits = tuple(int(s) for s in splits)
+        self.local_length = self.splits[self.rank]
+        self.sequence = sum(self.splits)
+        self.heads = heads
+        self.local_heads = heads // self.world
+        self.dim = dim
+        self._comm_stream = None
+
+    # -- plain transforms ----------------------------------------------------------
+    def sequence_to_heads(self, tensor: torch.Tensor) -> torch.Tensor:
+        """[L_r, H, D] -> [S, H/P, D]."""
+        L, hl, d = self.local_length, self.local_heads, self.dim
+        send = tensor.reshape(L, self.world, hl, d).permute(1, 0, 2, 3).contiguous().reshape(-1)
+        recv = torch.empty(self.sequence * hl * d, device=tensor.device, dtype=tensor.dtype)
+        dist.all_to_all_single(recv, send,
+                               output_split_sizes=[s * hl * d for s in self.splits],
+                               input_split_sizes=[L * hl * d] * self.world, group=self.group)
+        return recv.view(self.sequence, hl, d)
+
+    def heads_to_sequence(self, tensor: torch.Tensor) -> torch.Tensor:
+        """[S, H/P, D] -> [L_r, H, D]."""
+        L, hl, d = self.local_length, self.local_heads, self.dim
+        send = tensor.contiguous().reshape(-1)  # rows are already grouped by owner rank
+        recv = torch.empty(self.world * L * hl * d, device=tensor.device, dtype=tensor.dtype)
+        dist.all_to_all_single(recv, send,
+                               output_split_sizes=[L * hl * d] * self.world,
+                               input_split_sizes=[s * hl * d for s in self.splits],
+                               group=self.group)
+        return recv.view(self.world, L, hl, d).permute(1, 0, 2, 3).reshape(L, self.heads, d)
+
+    # -- packed QKV head chunks ------------------------------------------------------
+    def pack_chunk(self, qkv: torch.Tensor, start: int, stop: int, async_op: bool):
+        """qkv is the packed projection output [L_r, 3, H, D].  Sends heads
+        [start, stop) of every rank's head group as [world, L_r, c, 3, D] and receives
+        [S, c, 3, D].  Returns (receive, send, work)."""
+        L, hl, d = self.local_length, self.local_heads, self.dim
+        c = stop - start
+        src = qkv.view(L, 3, self.world, hl, d)[:, :, :, start:stop]      # [L,3,P,c,D]
+        send = torch.empty((self.world, L, c, 3, d), device=qkv.device, dtype=qkv.dtype)
+        send.copy_(src.permute(2, 0, 3, 1, 4))
+        recv = torch.empty((self.sequence, c, 3, d), device=qkv.device, dtype=qkv.dtype)
+        work = dist.all_to_all_single(recv.reshape(-1), send.reshape(-1),
+                                      output_split_sizes=[s * c * 3 * d for s in self.splits],
+                                      input_split_sizes=[L * c * 3 * d] * self.world,
+                                      group=self.group, async_op=async_op)
+        return recv, send, work
+
+    @staticmethod
+    def chunk_views(recv: torch.Tensor):
+        """[S, c, 3, D] -> q, k, v as [1, c, S, D] views with strides (., 384, c*384, 1)."""
+        q, k, v = recv.unbind(dim=2)
+        return tuple(t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+
+    # -- attention variants -------------------------------------------------------------
+    def attention_baseline(self, qkv: torch.Tensor, attn: Callable) -> torch.Tensor:
+        """Three all-to-alls, one attention over the local heads, reverse all-to-all.
+        `attn(q,k,v)` maps [1,h,S,D] views to a [1,h,S,D] view of [1,S,h,D] storage."""
+        parts = [self.sequence_to_heads(qkv[:, i]) for i in range(3)]
+        q, k, v = (t.transpose(0, 1).unsqueeze(0) for t in parts)
+        out = attn(q, k, v)
+        return self.heads_to_sequence(out.transpose(1, 2).reshape(self.sequence, self.local_heads,
+                                                                  self.dim))
+
+    def attention_fused(self, qkv: torch.Tensor, attn: Callable, chunks: int = 1,
+                        overlap: bool = False) -> torch.Tensor:
+        """One packed all-to-all per head chunk; with `overlap` the all-to-alls run on a
+        side stream and chunk i's attention overlaps chunk i+1's transfer."""
+        hl = self.local_heads
+        if hl % chunks:
+            raise RuntimeError("chunk count must divide the local head count")
+        step = hl // chunks
+        bounds = [(i * step, (i + 1) * step) for i in range(chunks)]
+        outputs = []
+        if overlap and qkv.is_cuda:
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=qkv.device)
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(qkv.device))
+            pending = []
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ready)
+                for a, b in bounds:
+                    item = self.pack_chunk(qkv, a, b, async_op=True)
+                    done = torch.cuda.Event()
+                    item[2].wait()          # orders the side stream after the collective
+                    done.record(self._comm_stream)
+                    pending.append((item, done))
+            for (recv, send, _work), done in pending:
+                torch.cuda.current_stream(qkv.device).wait_event(done)
+                recv.record_stream(torch.cuda.current_stream(qkv.device))
+                send.record_stream(self._comm_stream)
+                outputs.append(attn(*self.chunk_views(recv)))
+        else:
+            for a, b in bounds:
+                recv, _send, work = self.pack_chunk(qkv, a, b, async_op=False)
+                outputs.append(attn(*self.chunk_views(recv)))
+        # each output is a [1,c,S,D] view of [1,S,c,D] storage
+        seq_major = [o.transpose(1, 2).reshape(self.sequence, -1, self.dim) for o in outputs]
+        merged = seq_major[0] if len(seq_major) == 1 else torch.cat(seq_major, dim=1)
+        return self.heads_to_sequence(merged)

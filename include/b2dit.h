@@ -1,0 +1,152 @@
+/*
+ * b2dit.h - C ABI of libb2dit.so, the sm_100a implementation of the DiT hot path.
+ *
+ * Plain C: raw device pointers, sizes, element strides, a CUDA stream handle
+ * (cudaStream_t passed as void*).  No torch types.  Every entry point
+ *   - validates its arguments BEFORE launching anything and returns a b2_status,
+ *   - never allocates or frees device memory (the caller owns every buffer),
+ *   - enqueues its kernels on `stream` and returns without synchronising.
+ * On a non-zero status b2_last_error() holds a thread-local message.
+ *
+ * Each declaration cites the reference interface it replaces (path within the
+ * reference project : line).
+ */
+#ifndef B2DIT_H_
+#define B2DIT_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_ABI_VERSION 1
+
+typedef enum b2_status {
+  B2_OK = 0,
+  B2_BAD_DTYPE = 1,        /* bias_kind / activation code out of range            */
+  B2_BAD_SHAPE = 2,        /* negative, zero where forbidden, or inconsistent size */
+  B2_BAD_STRIDE = 3,       /* misaligned pointer or stride                         */
+  B2_NOT_WHITELISTED = 4,  /* shape outside what the kernel family supports        */
+  B2_LAUNCH_FAILED = 5,    /* cudaGetLastError() after the launch was non-zero     */
+  B2_TIMEOUT = 6,          /* a bounded device-side wait gave up                   */
+  B2_NULL_POINTER = 7,
+  B2_TOO_LARGE = 8         /* size beyond a documented static limit                */
+} b2_status;
+
+/* bias_kind: kernels/int8-epilogue/epilogue_kernel.hip:13-17 (enum BiasKind) */
+#define B2_BIAS_NONE 0
+#define B2_BIAS_BF16 1
+#define B2_BIAS_FP32 2
+
+/* input activation applied before quantisation,
+ * launcher/benchmark_launcher_v14_hires_int8_candidate.py:976 (`input_act`) */
+#define B2_ACT_NONE 0
+#define B2_ACT_SWIGLU 1
+
+int b2_version(void);
+const char* b2_last_error(void);
+const char* b2_status_string(int status);
+
+/* Reads the device-side error word (set by bounded waits that gave up) and
+ * clears it.  Synchronises `stream`.  Returns B2_OK or B2_TIMEOUT. */
+int b2_check_device_status(void* stream);
+
+/* Rowwise bf16 -> int8 quantizer.
+ * Replaces h3_quantize_int8_rowwise_hip, kernels/exact-rowwise-int8/quantizer_kernel.hip:118-144
+ * (Python: quantize_int8_rowwise(x) -> [q, scale], kernels/exact-rowwise-int8/quantizer.cpp:5-9).
+ * x bf16 [M,K] contiguous; q int8 [M,K]; scale fp32 [M] (the reference's [M,1]).
+ * M == 0 or K == 0 is legal: with M != 0 and K == 0 the scales are filled with 1e-30. */
+int b2_quantize_int8_rowwise(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
+                             void* stream);
+
+/* INT8 dequant epilogue, scalar contract with optional bias.
+ * Replaces h3_epilogue_hip, kernels/int8-epilogue/epilogue_kernel.hip:65-133
+ * (Python: epilogue(acc,row_scale,col_scale,bias), kernels/int8-epilogue/epilogue.cpp:9-13).
+ * The reference's M <= 65535 launch limit (:85-86) does not exist here. */
+int b2_epilogue(const int32_t* acc, const float* row_scale, const float* col_scale,
+                const void* bias, int bias_kind, void* out_bf16, int64_t M, int64_t N,
+                void* stream);
+
+/* INT8 dequant epilogue, bias-less 4-wide contract.
+ * Replaces h3_epilogue_vec4_hip, kernels/int8-epilogue-vec4/epilogue_kernel.hip:33-48
+ * (Python: epilogue(acc,row,col), kernels/int8-epilogue-vec4/epilogue.cpp:3-5). */
+int b2_epilogue_vec4(const int32_t* acc, const float* row_scale, const float* col_scale,
+                     void* out_bf16, int64_t M, int64_t N, void* stream);
+
+/* In-place x = bf16(bf16(x*bf16(1+scale[c])) + shift[c]).
+ * Replaces h3_mod_scale_shift_hip, kernels/mod-scale-shift/mod_kernel.hip:24-38
+ * (Python: mod_scale_shift_(x,scale,shift), kernels/mod-scale-shift/mod.cpp:3-5). */
+int b2_mod_scale_shift(void* x_bf16, const void* scale_bf16, const void* shift_bf16, int64_t M,
+                       int64_t C, void* stream);
+
+/* Fused SwiGLU + rowwise quantizer: x bf16 [M,2K] -> q int8 [M,K], scale fp32 [M].
+ * Replaces h3_swiglu_quantize_int8_rowwise_hip, kernels/swiglu-quant/swiglu_quant_kernel.hip:111-137
+ * (Python: swiglu_quantize_int8_rowwise(x), kernels/swiglu-quant/swiglu_quant.cpp:5-9). */
+int b2_swiglu_quantize_int8_rowwise(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
+                                    void* stream);
+
+/* acc[M,N] (int32) = A[M,K] . W[N,K]^T, both int8 row-major (K contiguous).
+ * Replaces the library GEMM call torch._int_mm(x_8, weight.T),
+ * launcher/benchmark_launcher_v14_hires_int8_candidate.py:805-824.
+ * Requires K % 16 == 0 and N % 4 == 0 (TMA 16-byte rules); any M >= 1. */
+int b2_int8_gemm(const int8_t* A, const int8_t* W, int32_t* acc, int64_t M, int64_t N, int64_t K,
+                 void* stream);
+
+/* GEMM with the dequant epilogue fused: out bf16 [M,N] =
+ *   bf16( bf16(float(acc)*(rs[m]*cs[n])) + bf16(bias[n]) ).
+ * Replaces steps 5+6 of _int8_linear_nocopy,
+ * launcher/benchmark_launcher_v14_hires_int8_candidate.py:1007-1052.
+ * Requires K % 16 == 0 and N % 8 == 0. */
+int b2_int8_gemm_dequant(const int8_t* A, const float* row_scale, const int8_t* W,
+                         const float* col_scale, const void* bias, int bias_kind, void* out_bf16,
+                         int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Whole INT8 linear: (activation) -> rowwise quantise -> GEMM -> dequant epilogue.
+ * Replaces _int8_linear_nocopy, launcher/benchmark_launcher_v14_hires_int8_candidate.py:960-1067
+ * (bf16 output, per-output-channel weight scale, no ConvRot).
+ * x bf16 [M,K] (act none) or [M,2K] (act swiglu); W int8 [N,K]; col_scale fp32 [N].
+ * q_scratch int8 [M,K] and s_scratch fp32 [M] are caller-provided scratch. */
+int b2_int8_linear(const void* x_bf16, int input_act, const int8_t* W, const float* col_scale,
+                   const void* bias, int bias_kind, void* out_bf16, int8_t* q_scratch,
+                   float* s_scratch, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* bf16 FlashAttention forward, non-causal, head_dim 128.
+ * Replaces h3_flash_fwd_bhsd, kernels/flash-attention-gfx936/csrc/flash_attn_hipc/h3_flash_api.cpp:30-130
+ * (Python: fwd_bhsd(q,k,v,softmax_scale), :133-142).
+ * q,k,v: logical [B,H,S,128] bf16 with element strides (batch, head, row) and a
+ * contiguous last dimension; strides must be multiples of 8 elements and pointers
+ * 16-byte aligned.  out: contiguous [B,S,H,128] bf16 (the reference's BSHD backing
+ * storage, :65-69).  softmax_scale finite and > 0. */
+int b2_flash_fwd(const void* q, const void* k, const void* v, void* out, int32_t B, int32_t H,
+                 int32_t S, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                 int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s, int64_t v_stride_b,
+                 int64_t v_stride_h, int64_t v_stride_s, float softmax_scale, void* stream);
+
+/* ---- DiT-block glue.  The reference has no source for these (they live in the
+ * host application's model file); conventions are this library's own. ---------- */
+
+/* out = bf16(LayerNorm_noaffine_fp32(x)) then mod-scale-shift's three roundings;
+ * x bf16 [M,C], out bf16 [M,C] (may alias x). */
+int b2_layernorm_mod(const void* x_bf16, const void* scale_bf16, const void* shift_bf16,
+                     void* out_bf16, int64_t M, int64_t C, float eps, void* stream);
+
+/* Same, followed by the rowwise quantizer: writes q int8 [M,C] and scale fp32 [M]. */
+int b2_layernorm_mod_quant(const void* x_bf16, const void* scale_bf16, const void* shift_bf16,
+                           int8_t* q, float* scale_out, int64_t M, int64_t C, float eps,
+                           void* stream);
+
+/* Per-head RMSNorm (weight bf16 [128]) + rotary on adjacent pairs, in place on the
+ * q and k parts of a packed qkv bf16 [S, 3, H, 128] buffer.  cos/sin fp32 [S,64]. */
+int b2_qk_norm_rope(void* qkv_bf16, const void* q_weight_bf16, const void* k_weight_bf16,
+                    const float* cos_tab, const float* sin_tab, int64_t S, int32_t H, float eps,
+                    void* stream);
+
+/* x = bf16(x + bf16(gate[c]*y)) in place on x; x,y bf16 [M,C], gate bf16 [C]. */
+int b2_gate_residual(void* x_bf16, const void* y_bf16, const void* gate_bf16, int64_t M, int64_t C,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2DIT_H_ */
