@@ -59,12 +59,28 @@ __device__ __forceinline__ float row_allreduce_nanmax(float v, float* smem) {
 // One row per TPR threads, VPT vectors of 8 bf16 per thread; C % 8 == 0,
 // C <= TPR*VPT*8.  QUANT selects the fused quantizer output.
 template <int TPR, int VPT, bool QUANT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scale,
                      const uint4* __restrict__ shift, uint4* __restrict__ out_bf16,
                      uint2* __restrict__ out_q, float* __restrict__ out_scale, int64_t M, int cvec,
                      float inv_c, float eps) {
   __shared__ float red[kThreads / 32];
+  // per-column operands staged once per CTA: factor = bf16(1+scale) and shift, packed
+  // like the data (8 bf16 per uint4)
+  extern __shared__ uint4 colvec[];
+  uint4* fac_s = colvec;
+  uint4* shf_s = colvec + cvec;
+  for (int c = threadIdx.x; c < cvec; c += kThreads) {
+    const uint4 sc = scale[c];
+    uint4 f;
+    f.x = pack_bf16x2_rn(__fadd_rn(1.0f, bf16lo_to_f32(sc.x)), __fadd_rn(1.0f, bf16hi_to_f32(sc.x)));
+    f.y = pack_bf16x2_rn(__fadd_rn(1.0f, bf16lo_to_f32(sc.y)), __fadd_rn(1.0f, bf16hi_to_f32(sc.y)));
+    f.z = pack_bf16x2_rn(__fadd_rn(1.0f, bf16lo_to_f32(sc.z)), __fadd_rn(1.0f, bf16hi_to_f32(sc.z)));
+    f.w = pack_bf16x2_rn(__fadd_rn(1.0f, bf16lo_to_f32(sc.w)), __fadd_rn(1.0f, bf16hi_to_f32(sc.w)));
+    fac_s[c] = f;
+    shf_s[c] = shift[c];
+  }
+  __syncthreads();
   constexpr int RPC = kThreads / TPR;
   const int slot = threadIdx.x / TPR;
   const int lane = threadIdx.x % TPR;
@@ -104,15 +120,14 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + i * TPR;
       if (c < cvec) {
-        const uint4 sc = scale[c], sh = shift[c];
-        const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+        const uint4 fc = fac_s[c], sh = shf_s[c];
+        const uint32_t fcw[4] = {fc.x, fc.y, fc.z, fc.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
         uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint32_t n = pack_bf16x2_rn((bf16lo_to_f32(w[j]) - mean) * rstd,
                                             (bf16hi_to_f32(w[j]) - mean) * rstd);
-          const float f0 = round_bf16_f32(__fadd_rn(1.0f, bf16lo_to_f32(scw[j])));
-          const float f1 = round_bf16_f32(__fadd_rn(1.0f, bf16hi_to_f32(scw[j])));
+          const float f0 = bf16lo_to_f32(fcw[j]), f1 = bf16hi_to_f32(fcw[j]);
           const uint32_t p = pack_bf16x2_rn(__fmul_rn(bf16lo_to_f32(n), f0),
                                             __fmul_rn(bf16hi_to_f32(n), f1));
           w[j] = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(p), bf16lo_to_f32(shw[j])),
@@ -196,24 +211,26 @@ int launch_layernorm_mod(const void* x, const void* scale, const void* shift, vo
                          bool quant, cudaStream_t stream) {
   const int cvec = (int)(C / 8);
   const float inv_c = 1.0f / (float)C;
+  const size_t smem_bytes = (size_t)cvec * 2 * sizeof(uint4);  // <= 32 KB for C <= 8192
 #define B2_LN(TPR, VPT)                                                                          \
   do {                                                                                           \
-    const int g = grid_for_rows(M, kThreads / TPR, 4);                                           \
+    const int g = grid_for_rows(M, kThreads / TPR, 8);                                           \
     if (quant)                                                                                   \
-      layernorm_mod_kernel<TPR, VPT, true><<<g, kThreads, 0, stream>>>(                          \
+      layernorm_mod_kernel<TPR, VPT, true><<<g, kThreads, smem_bytes, stream>>>(                          \
           (const uint4*)x, (const uint4*)scale, (const uint4*)shift, nullptr, (uint2*)out_q,     \
           out_scale, M, cvec, inv_c, eps);                                                       \
     else                                                                                         \
-      layernorm_mod_kernel<TPR, VPT, false><<<g, kThreads, 0, stream>>>(                         \
+      layernorm_mod_kernel<TPR, VPT, false><<<g, kThreads, smem_bytes, stream>>>(                         \
           (const uint4*)x, (const uint4*)scale, (const uint4*)shift, (uint4*)out_bf16, nullptr,  \
           nullptr, M, cvec, inv_c, eps);                                                         \
   } while (0)
   if (C <= 1024) B2_LN(32, 4);
-  else if (C <= 2048) B2_LN(64, 4);
-  else if (C <= 4096) B2_LN(128, 4);
-  else if (C <= 8192) B2_LN(256, 4);
-  else if (C <= 16384) B2_LN(256, 8);
-  else return fail(B2_NOT_WHITELISTED, "layernorm_mod: C=%lld exceeds 16384", (long long)C);
+  else if (C <= 2048) B2_LN(32, 8);
+  else if (C <= 3072) B2_LN(32, 12);
+  else if (C <= 4096) B2_LN(64, 8);
+  else if (C <= 6144) B2_LN(64, 12);
+  else if (C <= 8192) B2_LN(128, 8);
+  else return fail(B2_NOT_WHITELISTED, "layernorm_mod: C=%lld exceeds 8192", (long long)C);
 #undef B2_LN
   return check_launch("layernorm_mod");
 }

@@ -1,0 +1,167 @@
+"""bf16 FlashAttention forward on the GPU against fp32 math attention.
+
+Envelope: max-abs error <= 2e-4 for N(0,1) inputs (the reference's audited
+envelope, docs/hires-1344x768-campaign.md:19 in the reference: 1.9e-4 at 23638
+tokens), zero non-finite outputs.  Shapes follow the reference's gates:
+benchmarks/bench_opendas_h3_flash_bshd.py:142-165 (small, ragged tails, strided)
+and validation/validate_flash_longseq.py:28-71 (production stride family, sampled
+row blocks of heads {0, H/2, H-1})."""
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ENVELOPE = 2e-4
+GOLD = Path(__file__).parent / "golden"
+
+
+def make_qkv(seq, heads, seed, layout="standard"):
+    """fp32 randn -> bf16, as [1,H,S,128] views of the layout's storage."""
+    g = torch.Generator().manual_seed(seed)
+    if layout == "standard":        # [S, H*128] storage
+        return tuple(torch.randn(seq, heads * 128, generator=g).to(torch.bfloat16)
+                     .view(1, seq, heads, 128).permute(0, 2, 1, 3) for _ in range(3))
+    if layout == "contiguous":      # [1,H,S,128] storage
+        return tuple(torch.randn(1, heads, seq, 128, generator=g).to(torch.bfloat16) for _ in range(3))
+    if layout == "chunk":           # packed all-to-all receive buffer [S, c, 3, 128]
+        buf = torch.randn(seq, heads, 3, 128, generator=g).to(torch.bfloat16)
+        return tuple(t.transpose(0, 1).unsqueeze(0) for t in buf.unbind(dim=2))
+    if layout == "qkv":             # packed projection output [S, 3, H, 128]
+        buf = torch.randn(seq, 3, heads, 128, generator=g).to(torch.bfloat16)
+        return tuple(buf[:, i].transpose(0, 1).unsqueeze(0) for i in range(3))
+    raise ValueError(layout)
+
+
+def to_dev(t):
+    """Move while preserving the exact strides."""
+    flat = torch.empty(t.untyped_storage().size() // 2, dtype=t.dtype)
+    flat.set_(t.untyped_storage(), 0, (t.untyped_storage().size() // 2,), (1,))
+    return torch.as_strided(flat.to(DEV), t.shape, t.stride(), t.storage_offset())
+
+
+@pytest.mark.parametrize("seq,layout", [(128, "contiguous"), (129, "standard"), (257, "standard"),
+                                        (512, "standard"), (1024, "standard"), (1, "standard"),
+                                        (127, "chunk"), (300, "chunk"), (385, "qkv"), (256, "contiguous")])
+def test_small_gate(cuda_pkg, ref, seq, layout):
+    heads = 4
+    q, k, v = make_qkv(seq, heads, 100 + seq, layout)
+    want = ref.attention_fp32(q, k, v, 128 ** -0.5)
+    qd, kd, vd = to_dev(q), to_dev(k), to_dev(v)
+    assert qd.stride() == q.stride()
+    out = cuda_pkg.ops.fwd_bhsd(qd, kd, vd, 128 ** -0.5)
+    cuda_pkg.ops.check_device_status()
+    assert out.shape == (1, heads, seq, 128)
+    assert out.transpose(1, 2).is_contiguous()                      # BSHD backing storage
+    flat = out.transpose(1, 2).flatten(start_dim=2)
+    assert flat.untyped_storage().data_ptr() == out.untyped_storage().data_ptr()  # free view
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    err = float((got - want).abs().max())
+    # small sequences have O(1) outputs dominated by a few keys: bf16 rounding of P and
+    # of the output (2^-9 relative each) does not average out, so bound by the envelope
+    # scaled with the output magnitude (2^-7 relative)
+    bound = max(ENVELOPE, float(want.abs().max()) * 2 ** -7)
+    assert err <= bound, (seq, layout, err, bound)
+    out2 = cuda_pkg.ops.fwd_bhsd(qd, kd, vd, 128 ** -0.5)
+    assert torch.equal(out, out2)                                   # deterministic
+
+
+def test_golden_fixture_from_reference_fp32(cuda_pkg):
+    z = np.load(GOLD / "attention_fp32.npz")
+    for idx in range(2):
+        q, k, v = (torch.from_numpy(z[f"a{idx}_{n}"].astype(np.int16)).view(torch.bfloat16) for n in "qkv")
+        out = cuda_pkg.ops.fwd_bhsd(q.to(DEV), k.to(DEV), v.to(DEV), 128 ** -0.5).float().cpu()
+        want = torch.from_numpy(z[f"a{idx}_rows_h0"])
+        bound = max(ENVELOPE, float(want.abs().max()) * 2 ** -7)
+        assert float((out[0, 0] - want).abs().max()) <= bound
+
+
+def test_errors(cuda_pkg):
+    ops = cuda_pkg.ops
+    q = torch.zeros((1, 2, 16, 128), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="head dimension 128"):
+        ops.fwd_bhsd(q[..., :64], q[..., :64], q[..., :64], 0.1)
+    with pytest.raises(RuntimeError, match="identical QKV shapes"):
+        ops.fwd_bhsd(q, q[:, :1], q, 0.1)
+    with pytest.raises(RuntimeError, match="finite and positive"):
+        ops.fwd_bhsd(q, q, q, 0.0)
+    with pytest.raises(RuntimeError, match="BF16"):
+        ops.fwd_bhsd(q.half(), q.half(), q.half(), 0.1)
+    with pytest.raises(RuntimeError, match="contiguous last"):
+        t = torch.zeros((1, 2, 128, 16), dtype=torch.bfloat16, device=DEV).transpose(2, 3)
+        ops.fwd_bhsd(t, t, t, 0.1)
+
+
+def _device_rows_fp32(q, k, v, head, r0, r1, scale):
+    """fp32 math attention for a row block, computed by torch on the device."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        qf, kf, vf = q[0, head, r0:r1].float(), k[0, head].float(), v[0, head].float()
+        return torch.softmax((qf @ kf.T) * scale, dim=-1) @ vf
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+@pytest.mark.parametrize("seq,heads", [(23638, 24), (109099, 3)])
+def test_production_shapes_sampled_rows(cuda_pkg, ref, seq, heads):
+    """Config 2 (23638 x 24 heads) and the 8-GPU shard of config 5 (109099 x 3 heads)."""
+    g = torch.Generator(device=DEV).manual_seed(1000 + seq)
+    mk = lambda: (torch.randn(seq, heads * 128, device=DEV, dtype=torch.float32, generator=g)
+                  .to(torch.bfloat16).view(1, seq, heads, 128).permute(0, 2, 1, 3))
+    q, k, v = mk(), mk(), mk()
+    scale = 128 ** -0.5
+    out = cuda_pkg.ops.fwd_bhsd(q, k, v, scale)
+    cuda_pkg.ops.check_device_status()
+    assert int((~torch.isfinite(out.float())).sum()) == 0
+    worst = 0.0
+    chunk = 2048
+    for head in sorted({0, heads // 2, heads - 1}):
+        for r0 in (0, seq // 2, max(0, seq - chunk)):
+            r1 = min(seq, r0 + chunk)
+            want = _device_rows_fp32(q, k, v, head, r0, r1, scale)
+            worst = max(worst, float((out[0, head, r0:r1].float() - want).abs().max()))
+    assert worst <= ENVELOPE, worst
+    # one block against the CPU oracle as well (same recipe as the reference's validator)
+    r0 = seq // 2
+    want_cpu = ref.attention_rows_fp32(q.cpu(), k.cpu(), v.cpu(), heads - 1, r0, r0 + 256, scale)
+    assert float((out[0, heads - 1, r0:r0 + 256].float().cpu() - want_cpu).abs().max()) <= ENVELOPE
+    digest = hashlib.sha256(out.cpu().view(torch.int16).numpy().tobytes()).hexdigest()
+    out2 = cuda_pkg.ops.fwd_bhsd(q, k, v, scale)
+    assert hashlib.sha256(out2.cpu().view(torch.int16).numpy().tobytes()).hexdigest() == digest
+
+
+def test_strided_layouts_are_bitwise_equal_to_contiguous(cuda_pkg):
+    """The reference requires interleaved-stride and contiguous attention to agree
+    bitwise (benchmarks/bench_sp_head_chunk_overlap.py:275-282 in the reference)."""
+    g = torch.Generator().manual_seed(9)
+    buf = torch.randint(-8, 9, (700, 3, 3, 128), generator=g).to(torch.bfloat16).to(DEV)  # [S,c,3,D]
+    q, k, v = (t.transpose(0, 1).unsqueeze(0) for t in buf.unbind(dim=2))
+    assert tuple(q.stride()[1:]) == (384, 3 * 384, 1)
+    a = cuda_pkg.ops.fwd_bhsd(q, k, v, 128 ** -0.5)
+    b = cuda_pkg.ops.fwd_bhsd(q.contiguous(), k.contiguous(), v.contiguous(), 128 ** -0.5)
+    assert torch.equal(a, b)
+
+
+def test_gated_attention_entry(cuda_pkg):
+    pkg = cuda_pkg
+    pkg._lib.admit()
+    g = pkg.gates.Gates.all_on()
+    calls = []
+    g.register_fallbacks(attention=lambda q, k, v, heads, **kw: calls.append(kw) or "host")
+    S, H = 300, 24
+    buf = torch.randn(S, 3, H, 128, device=DEV).to(torch.bfloat16)
+    q, k, v = (buf[:, i].transpose(0, 1).unsqueeze(0) for i in range(3))
+    sp = pkg.attention.SPContext(0, 1, (S,), S)
+    out = pkg.attention.attention(q, k, v, H, skip_reshape=True, gates=g, sp_context=sp)
+    assert out.shape == (1, S, H * 128) and g.counters["flash"].hits == 1
+    out4 = pkg.attention.attention(q, k, v, H, skip_reshape=True, skip_output_reshape=True, gates=g, sp_context=sp)
+    assert out4.shape == (1, H, S, 128)
+    assert pkg.attention.attention(q, k, v, H, mask=torch.ones(1), skip_reshape=True, gates=g, sp_context=sp) == "host"
+    assert pkg.attention.attention(q, k, v, H, skip_reshape=False, gates=g, sp_context=sp) == "host"
+    assert g.dump_counters()["flash"]["reasons"] == {"mask": 1, "skip_reshape": 1}
+    assert len(g.flash_fallback_signatures) == 2
