@@ -111,6 +111,20 @@ int b2_int8_linear(const void* x_bf16, int input_act, const int8_t* W, const flo
                    const void* bias, int bias_kind, void* out_bf16, int8_t* q_scratch,
                    float* s_scratch, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* The same linear for callers that cannot supply scratch memory: hosts whose own pool
+ * already owns all device memory, plugins that only receive their input and output
+ * buffers, serving loops that must not allocate once running.  The quantised activation and
+ * its scales live in a fixed array inside the library (32 MiB + 256 KiB, held by every GPU
+ * that loads the library until the process exits).  Limits: M <= 65536 and M*K <= 32 MiB,
+ * otherwise B2_TOO_LARGE.  All calls on a GPU share that array and it keeps the previous
+ * call's contents (nothing in it needs to start at zero): calls that can overlap on the GPU
+ * race, so serialise them.  The first call on each device resolves the array's address;
+ * make it during start-up, before any stream capture.  Allocates nothing.
+ * This entry point has no counterpart in the reference project. */
+int b2_int8_linear_noalloc(const void* x_bf16, int input_act, const int8_t* W,
+                           const float* col_scale, const void* bias, int bias_kind, void* out_bf16,
+                           int64_t M, int64_t N, int64_t K, void* stream);
+
 /* bf16 FlashAttention forward, non-causal, head_dim 128.
  * Replaces h3_flash_fwd_bhsd, kernels/flash-attention-gfx936/csrc/flash_attn_hipc/h3_flash_api.cpp:30-130
  * (Python: fwd_bhsd(q,k,v,softmax_scale), :133-142).
