@@ -1,0 +1,99 @@
+"""Ulysses sequence parallelism on real GPUs (NCCL), one process per GPU.
+
+Needs >= 2 GPUs (skipped otherwise).  Inputs are small integers cast to bf16 so they
+are exactly representable and any stream-ordering hazard shows up as a bit mismatch,
+as in the reference's distributed probe (benchmarks/bench_sp_head_chunk_overlap.py:75-81,
+:196-199, :264-323 in the reference): every variant must be bitwise equal on all
+ranks, and equal to the single-GPU result."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, seq, result_dir):
+    sys.path.insert(0, str(ROOT))
+    import importlib
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        pkg = importlib.import_module("dcu-video-dit-turbo_b200")
+        from oracle import ref_ops as ref
+        ops = pkg.ops
+        H, D = 24, 128
+        splits = pkg.ulysses.sequence_splits(seq, world)
+        sp = pkg.ulysses.UlyssesSP(splits, H, D)
+        pkg.gates.agree_flag_across_ranks(True)
+        g = torch.Generator().manual_seed(20260812)
+        qkv_full = torch.randint(-8, 9, (seq, 3, H, D), generator=g).to(torch.bfloat16)
+        row0 = sum(splits[:rank])
+        mine = qkv_full[row0:row0 + splits[rank]].contiguous().to(dev)
+        attn = lambda q, k, v: ops.fwd_bhsd(q, k, v, D ** -0.5)
+        # single-GPU attention over the full sequence (every rank computes it locally)
+        full = qkv_full.to(dev)
+        q, k, v = (full[:, i].transpose(0, 1).unsqueeze(0) for i in range(3))
+        single = attn(q, k, v).transpose(1, 2).reshape(seq, H, D)[row0:row0 + splits[rank]]
+        hl = H // world
+        results = {"baseline": sp.attention_baseline(mine, attn),
+                   "fused1": sp.attention_fused(mine, attn, chunks=1, overlap=False),
+                   "fused_serial": sp.attention_fused(mine, attn, chunks=min(hl, 3), overlap=False),
+                   "fused_overlap": sp.attention_fused(mine, attn, chunks=min(hl, 3), overlap=True),
+                   "fused_overlap_max": sp.attention_fused(mine, attn, chunks=hl, overlap=True)}
+        torch.cuda.synchronize()
+        ok = all(torch.equal(t, single) for t in results.values())
+        flag = torch.tensor([int(ok)], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        bad = [n for n, t in results.items() if not torch.equal(t, single)]
+        # the whole block: 2-GPU token shard vs the same rows of the 1-GPU block
+        params = pkg.block.make_block_params(seed=11, device=dev)
+        cos, sin = pkg.block.rope_tables(pkg.block.grid_positions(seq))
+        gx = torch.Generator().manual_seed(5)
+        x_full = torch.randn((seq, 3072), generator=gx).to(torch.bfloat16)
+        y_single = pkg.block.DiTBlock(params).forward(x_full.to(dev), cos.to(dev), sin.to(dev))
+        sl = slice(row0, row0 + splits[rank])
+        blk = pkg.block.DiTBlock(params, sp=sp, head_chunks=min(hl, 3), overlap=True)
+        y_sp = blk.forward(x_full[sl].to(dev), cos[sl].to(dev), sin[sl].to(dev))
+        torch.cuda.synchronize()
+        ops.check_device_status(dev)
+        block_equal = torch.equal(y_sp, y_single[sl])
+        psnr = ref.psnr(y_single[sl].float().cpu(), y_sp.float().cpu())
+        Path(result_dir, f"r{rank}.txt").write_text(
+            f"attn_all_ranks={int(flag.item())} bad={bad} block_equal={block_equal} psnr={psnr}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seq", [1001, 4099])
+def test_ulysses_attention_and_block_bitwise_vs_single_gpu(tmp_path, seq):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 4 if n >= 4 else 2
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, seq, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        text = Path(tmp_path, f"r{r}.txt").read_text()
+        assert "attn_all_ranks=1" in text and "bad=[]" in text, text
+        # row-local int8 stages and per-head attention are partition invariant, so the block
+        # is expected bitwise equal; the published gate is PSNR (>= 60 dB, this project's
+        # choice: the reference gives no block-level threshold)
+        psnr = float(text.split("psnr=")[1])
+        assert psnr >= 60.0, text
+        assert "block_equal=True" in text, text
