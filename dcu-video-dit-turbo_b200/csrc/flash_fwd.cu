@@ -10,21 +10,25 @@
 //
 //   One CTA owns TWO 128-row query tiles of one (batch, head) and walks the KV
 //   sequence in 128-row steps.
-//     warps 0-3   softmax for query tile 0: one thread per row, S row read from
-//                 tensor memory into registers, online softmax, P written back to
-//                 tensor memory as bf16 (aliasing the S columns)
-//     warps 4-7   the same for query tile 1
-//     warp 8      MMA issuer: S = Q.K^T (tcgen05.mma kind::f16, operands in shared
-//                 memory) and O += P.V (P read from tensor memory, V from shared
-//                 memory as an MN-major operand); accumulators S0,S1,O0,O1 fill
-//                 the 512 tensor-memory columns
-//     warp 9      TMA loader: Q once, K and V tiles through a two-stage ring
-//                 (128-byte swizzle; plain per-CTA loads, no multicast)
-//   The two tiles ping-pong: while the softmax warps of one tile run exp2 the
-//   tensor core works on the other tile's MMAs.
-//   The O rescale is lazy: a row's running max is only raised (and O, l rescaled)
-//   when the new max exceeds it by more than 2^8 in the exp2 domain, so after the
-//   first steps the rescale almost never runs; the final O/l is exact either way.
+//     warp 0       MMA issuer: S = Q.K^T (tcgen05.mma kind::f16, operands in shared
+//                  memory) and O += P.V (P read from tensor memory, V from shared
+//                  memory as an MN-major operand); accumulators S0,S1,O0,O1 fill the
+//                  512 tensor-memory columns; descriptors are pre-built so that an MMA
+//                  costs the issuing thread three instructions
+//     warp 1       TMA loader: Q once, K and V tiles through a two-stage ring
+//                  (128-byte swizzle; plain per-CTA loads, no multicast)
+//     warps 2-9    softmax for query tile 0, TWO threads per row: warp w and warp w+4
+//                  read the same 32 tensor-memory lanes and split the 128 S columns
+//                  64/64, so two instruction streams share each scheduler and the
+//                  exp2 unit stays busy while either one is blocked
+//     warps 10-17  the same for query tile 1
+//   The two tiles ping-pong: while one tile's softmax runs, the tensor core works on
+//   the other tile's MMAs.  P overwrites S in place as bf16.
+//   Softmax runs against the running row max of the PREVIOUS steps, so the max is off
+//   the critical path; the running max is only raised (and O, l rescaled, P recomputed)
+//   when a new score exceeds it by more than 2^8 in the exp2 domain, which after the
+//   first steps almost never happens.  The two threads of a row agree on that through a
+//   shared-memory flag and a two-warp mbarrier handshake per step; the final O/l is exact.
 // Every mbarrier wait is bounded; on a timeout the kernel records a status word and
 // returns through the common teardown.
 #include <cmath>
@@ -45,19 +49,26 @@ constexpr int HEAD_DIM = 128;
 constexpr int HALF_BYTES = 128 * 128;        // one [128 rows x 64 bf16] swizzled half tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 320;
+constexpr int kMmaWarp = 0, kLoadWarp = 1, kFirstSoftmaxWarp = 2;
+constexpr int NUM_THREADS = (2 + 16) * 32;   // 576
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 384;
+#ifndef B2_FLASH_POLY_EVERY
+#define B2_FLASH_POLY_EVERY 0
+#endif
+constexpr int kPolyEvery = B2_FLASH_POLY_EVERY;  // every n-th pair takes the polynomial exp2 (0 = none)
 
 constexpr int SMEM_Q = 0;                                   // 2 tiles
 constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;             // KV_STAGES tiles
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;     // KV_STAGES tiles
-constexpr int SMEM_BARS = SMEM_V + KV_STAGES * TILE_BYTES;  // 16 mbarriers
-constexpr int SMEM_TOTAL = 1024 + SMEM_BARS + 16 * 8 + 16;
+constexpr int SMEM_BARS = SMEM_V + KV_STAGES * TILE_BYTES;  // 16 mbarriers + tmem slot + abort
+constexpr int NUM_BARS = 24;
+constexpr int SMEM_XCHG = SMEM_BARS + NUM_BARS * 8 + 16;    // flags [2][8] + row exchange [2][2][128]
+constexpr int SMEM_TOTAL = 1024 + SMEM_XCHG + 2 * 8 * 4 + 2 * 2 * 128 * 4;
 
 // mbarrier indices
 enum { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_FULL = 12,
-       O_FULL = 14 };
+       O_FULL = 14, PAIR_SYNC = 16 /* 8: one per (tile, lane quarter) */ };
 
 struct FlashArgs {
   __nv_bfloat16* out;  // [B, S, H, 128]
@@ -67,10 +78,27 @@ struct FlashArgs {
   float scale_log2;   // softmax_scale * log2(e)
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// exp2 on the FMA pipe: round to the nearest integer n with the 1.5*2^23 trick, a
+// degree-3 polynomial for 2^f on f = x - n in [-0.5, 0.5] (max relative error 1.6e-4,
+// below the bf16 rounding that P undergoes anyway), then n added into the exponent field.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(f, 0.05360212177038193f, 0.24237291514873505f);
+  p = fmaf(f, p, 0.6935023665428162f);
+  p = fmaf(f, p, 0.9999481439590454f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
 // rows x 64-element half tiles of one [128 x 128] bf16 tile
@@ -86,29 +114,23 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
   }
 }
 
-// S[128x128] = A[128 x 128(d)] . B[128 x 128(d)]^T, both K-major half-tile pairs
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_addr, uint32_t k_addr) {
-  constexpr uint32_t idesc = make_idesc(/*f32*/ 1, /*bf16*/ 1, /*bf16*/ 1, 0, 0, BLOCK_M, BLOCK_N);
+// Descriptor LOW-word tables of the MMA issuer, built once per CTA:
+//   Q (A of S = Q.K^T) and K (B): K-major half-tile pairs, 32 bytes of head dim per MMA;
+//   V (B of O += P.V): MN-major, 64-wide d blocks one half tile apart (LBO), 8-row kv
+//   groups 1024 bytes apart (SBO), 16 kv rows = 2048 bytes per MMA.
+__device__ __forceinline__ void build_kmajor_lo(uint32_t (&d)[8], uint32_t tile_addr) {
+  const uint32_t lo = desc_lo(tile_addr, 16);
 #pragma unroll
-  for (int i = 0; i < HEAD_DIM / 16; ++i) {
-    const uint32_t off = (i >> 2) * HALF_BYTES + (i & 3) * 32;
-    mma_f16_ss(d_tmem, make_smem_desc_sw128(q_addr + off, 16, 1024),
-               make_smem_desc_sw128(k_addr + off, 16, 1024), idesc, i != 0);
-  }
+  for (int i = 0; i < 8; ++i) d[i] = lo + (i >> 2) * (HALF_BYTES >> 4) + (i & 3) * 2;
+}
+__device__ __forceinline__ void build_v_lo(uint32_t (&d)[8], uint32_t tile_addr) {
+  const uint32_t lo = desc_lo(tile_addr, HALF_BYTES);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) d[i] = lo + i * (2048 >> 4);
 }
 
-// O[128x128(d)] (+)= P[128 x 128(kv)] (tensor memory, bf16) . V[128(kv) x 128(d)]
-// V is the MN-major B operand: 64-wide d blocks LBO = one half tile apart, 8-row kv
-// groups SBO = 1024 bytes apart; 16 kv rows per MMA = 2048 bytes.
-__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_addr,
-                                         bool accumulate) {
-  constexpr uint32_t idesc = make_idesc(1, 1, 1, 0, /*B MN-major*/ 1, BLOCK_M, HEAD_DIM);
-#pragma unroll
-  for (int i = 0; i < BLOCK_N / 16; ++i) {
-    mma_f16_ts(o_tmem, p_tmem + i * 8, make_smem_desc_sw128(v_addr + i * 2048, HALF_BYTES, 1024),
-               idesc, accumulate || i != 0);
-  }
-}
+constexpr uint32_t kIdescQK = make_idesc(/*f32*/ 1, /*bf16*/ 1, /*bf16*/ 1, 0, 0, BLOCK_M, BLOCK_N);
+constexpr uint32_t kIdescPV = make_idesc(1, 1, 1, 0, /*B MN-major*/ 1, BLOCK_M, HEAD_DIM);
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -117,8 +139,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BARS);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* redo_flags = reinterpret_cast<volatile int*>(smem + SMEM_XCHG);  // [2][8]
+  volatile float* xchg = reinterpret_cast<volatile float*>(smem + SMEM_XCHG + 2 * 8 * 4);  // [2][2][128]
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int idx) -> uint32_t { return bar0 + idx * 8; };
@@ -129,14 +153,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int n_kv = args.n_kv;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 128 : 1);
+    for (int i = 0; i < NUM_BARS; ++i)
+      mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 8 : (i >= PAIR_SYNC ? 2 : 1));
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  if (warp == 8) {
+  if (threadIdx.x < 16) redo_flags[threadIdx.x] = 0;
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
@@ -145,7 +171,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 9) {
+  if (warp == kLoadWarp) {
     // ------------------------------- TMA loader -------------------------------
     if (lane == 0) {
       const int q_row0 = pair * 2 * BLOCK_M;
@@ -165,145 +191,208 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                   args.v_swap);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      const uint32_t q0 = sbase + SMEM_Q, q1 = q0 + TILE_BYTES;
       const uint32_t s0 = tmem_base + COL_S0, s1 = tmem_base + COL_S1;
       const uint32_t o0 = tmem_base + COL_O0, o1 = tmem_base + COL_O1;
+      uint32_t q0[8], q1[8], kA[8], kB[8], vA[8], vB[8], pa0[8], pa1[8];
+      build_kmajor_lo(q0, sbase + SMEM_Q);
+      build_kmajor_lo(q1, sbase + SMEM_Q + TILE_BYTES);
+      build_kmajor_lo(kA, sbase + SMEM_K);
+      build_kmajor_lo(kB, sbase + SMEM_K + TILE_BYTES);
+      build_v_lo(vA, sbase + SMEM_V);
+      build_v_lo(vB, sbase + SMEM_V + TILE_BYTES);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        pa0[i] = s0 + i * 8;  // P: 8 tensor-memory columns (16 bf16 of kv) per MMA
+        pa1[i] = s1 + i * 8;
+      }
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, kStatusFlashTimeout) &&
                 mbar_wait(bar(K_FULL), 0, abort_flag, kStatusFlashTimeout);
       if (ok) {
         tc_fence_after();
-        issue_qk(s0, q0, sbase + SMEM_K);
+        mma_f16_ss_lo_x8(s0, q0, kA, kIdescQK);
         tc_commit(bar(S_FULL));
         ok = mbar_wait(bar(Q_FULL + 1), 0, abort_flag, kStatusFlashTimeout);
       }
       if (ok) {
         tc_fence_after();
-        issue_qk(s1, q1, sbase + SMEM_K);
+        mma_f16_ss_lo_x8(s1, q1, kA, kIdescQK);
         tc_commit(bar(S_FULL + 1));
         tc_commit(bar(K_EMPTY));
       }
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t v_addr = sbase + SMEM_V + st * TILE_BYTES;
+      // One kv step.  `st` (ring stage of step j) is a literal at both call sites so the
+      // tables are indexed at compile time; the next step's K sits in the other stage.
+      auto step = [&](const int j, const uint32_t (&vd)[8], const uint32_t (&kd_next)[8],
+                      const int st) -> bool {
         const bool last = j + 1 == n_kv;
-        const int st2 = (j + 1) & 1;
-        const uint32_t k_next = sbase + SMEM_K + st2 * TILE_BYTES;
-        if (!(ok = mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag, kStatusFlashTimeout))) break;
-        if (!(ok = mbar_wait(bar(P_FULL), j & 1, abort_flag, kStatusFlashTimeout))) break;
+        const int st2 = st ^ 1;
+        if (!mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
+        if (!mbar_wait(bar(P_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        issue_pv(o0, s0, v_addr, j != 0);
+        mma_f16_ts_lo_x8(o0, pa0, vd, kIdescPV, j != 0);
         if (last) {
           tc_commit(bar(O_FULL));
         } else {
-          if (!(ok = mbar_wait(bar(K_FULL + st2), ((j + 1) >> 1) & 1, abort_flag, kStatusFlashTimeout))) break;
+          if (!mbar_wait(bar(K_FULL + st2), ((j + 1) >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
           tc_fence_after();
-          issue_qk(s0, q0, k_next);
+          mma_f16_ss_lo_x8(s0, q0, kd_next, kIdescQK);
           tc_commit(bar(S_FULL));
         }
-        if (!(ok = mbar_wait(bar(P_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout))) break;
+        if (!mbar_wait(bar(P_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        issue_pv(o1, s1, v_addr, j != 0);
+        mma_f16_ts_lo_x8(o1, pa1, vd, kIdescPV, j != 0);
         tc_commit(bar(V_EMPTY + st));
         if (last) {
           tc_commit(bar(O_FULL + 1));
         } else {
-          issue_qk(s1, q1, k_next);
+          mma_f16_ss_lo_x8(s1, q1, kd_next, kIdescQK);
           tc_commit(bar(S_FULL + 1));
           tc_commit(bar(K_EMPTY + st2));
         }
+        return true;
+      };
+      for (int j = 0; ok && j < n_kv; j += 2) {
+        ok = step(j, vA, kB, 0);
+        if (ok && j + 1 < n_kv) ok = step(j + 1, vB, kA, 1);
       }
     }
   } else {
-    // ------------------------- softmax + output, one row per thread -------------------------
-    const int t = warp >> 2;        // query tile of this warpgroup
-    const int quarter = warp & 3;   // tensor-memory lane quarter
+    // ---------------- softmax + output: two threads per row, 64 columns each ----------------
+    const int ws = warp - kFirstSoftmaxWarp;
+    const int t = ws >> 3;              // query tile
+    const int half = (ws >> 2) & 1;     // which 64 of the 128 S / O columns
+    const int quarter = warp & 3;       // tensor-memory lane quarter of this warp
+    const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem_base + (t ? COL_S1 : COL_S0) + lane_sel;
-    const uint32_t o_tmem = tmem_base + (t ? COL_O1 : COL_O0) + lane_sel;
+    const uint32_t s_tmem = tmem_base + (t ? COL_S1 : COL_S0) + lane_sel + half * 64;
+    const uint32_t p_tmem = tmem_base + (t ? COL_S1 : COL_S0) + lane_sel + half * 32;
+    const uint32_t o_tmem = tmem_base + (t ? COL_O1 : COL_O0) + lane_sel + half * 64;
+    // The two warps that share a row group meet at a named barrier (bar.sync id, 64).
+    // bar.sync has no time limit, so the loop below never leaves early: after an abort a
+    // warp keeps walking the remaining steps, skips the waits and the arithmetic, and
+    // still executes every barrier its partner will execute (the count per step depends
+    // only on a flag both read after the first barrier).
+    const uint32_t pair_bar = 1 + t * 4 + quarter;
+    bool ok = true;
+    auto pair_sync = [&]() { named_barrier_sync(pair_bar, 64); };
+    volatile float* my_x = xchg + (t * 2 + half) * 128 + row_in_tile;
+    volatile float* other_x = xchg + (t * 2 + (half ^ 1)) * 128 + row_in_tile;
     const float sl2 = args.scale_log2;
     const int tail_valid = args.S - (n_kv - 1) * BLOCK_N;  // valid columns of the last step
-    float row_max = -INFINITY;  // raw-score domain, may lag the true max by < 2^8/sl2
-    float row_sum = 0.f;
-    bool ok = true;
+    float row_max = -INFINITY;  // raw-score domain, shared by both threads of the row
+    float row_sum = 0.f;        // this thread's 64 columns only
     for (int j = 0; j < n_kv; ++j) {
-      if (!(ok = mbar_wait(bar(S_FULL + t), j & 1, abort_flag, kStatusFlashTimeout))) break;
+      if (ok) ok = mbar_wait(bar(S_FULL + t), j & 1, abort_flag, kStatusFlashTimeout);
       tc_fence_after();
-      uint32_t sraw[128];
-      {
-        uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sraw[0]);
-        uint32_t(&c1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sraw[32]);
-        uint32_t(&c2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sraw[64]);
-        uint32_t(&c3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sraw[96]);
-        tmem_ld_32x32b_x32(s_tmem + 0, c0);
-        tmem_ld_32x32b_x32(s_tmem + 32, c1);
-        tmem_ld_32x32b_x32(s_tmem + 64, c2);
-        tmem_ld_32x32b_x32(s_tmem + 96, c3);
-        tmem_wait_ld();
-      }
-      if (j + 1 == n_kv && tail_valid < BLOCK_N) {
+      // columns of this thread that are valid in this step (tail masking)
+      const int valid = ((j + 1 == n_kv) ? tail_valid : BLOCK_N) - half * 64;
+      uint32_t p[32];
+      float tile_max, tile_sum;
+      // One pass over this thread's 64 S columns in four 16-column chunks, double buffered
+      // so the tensor-memory load of chunk k+1 overlaps the arithmetic of chunk k.
+      auto pass = [&](const bool do_exp) {
+        const float neg_ms = -row_max * sl2;
+        float mx[2] = {-INFINITY, -INFINITY};
+        float sm[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t buf[2][16];
+        tmem_ld_32x32b_x16(s_tmem, buf[0]);
 #pragma unroll
-        for (int c = 0; c < 128; ++c)
-          if (c >= tail_valid) sraw[c] = 0xff800000u;  // -inf
-      }
-      float m = __uint_as_float(sraw[0]);
+        for (int k = 0; k < 4; ++k) {
+          tmem_wait_ld();
+          if (k < 3) tmem_ld_32x32b_x16(s_tmem + 16 * (k + 1), buf[(k + 1) & 1]);
+          uint32_t(&v)[16] = buf[k & 1];
+          if (valid < 16 * (k + 1)) {
 #pragma unroll
-      for (int c = 1; c < 128; ++c) m = fmaxf(m, __uint_as_float(sraw[c]));
-      // lazy rescale: raise the running max only when it lags by more than 2^8
-      const bool raise = (m - row_max) * sl2 > 8.0f;  // true on the first step (row_max = -inf)
-      if (__any_sync(0xffffffffu, raise)) {
+            for (int c = 0; c < 16; ++c)
+              if (16 * k + c >= valid) v[c] = 0xff800000u;  // -inf
+          }
+#pragma unroll
+          for (int c = 0; c < 16; c += 2) {
+            const float a = __uint_as_float(v[c]), b2v = __uint_as_float(v[c + 1]);
+            mx[(c >> 1) & 1] = fmax3(mx[(c >> 1) & 1], a, b2v);
+            if (do_exp) {
+              float e0, e1;
+              if (kPolyEvery != 0 && ((c >> 1) % (kPolyEvery ? kPolyEvery : 1)) == 0) {
+                e0 = ex2_poly(fmaf(a, sl2, neg_ms));  // this pair's exp2 on the FMA pipe
+                e1 = ex2_poly(fmaf(b2v, sl2, neg_ms));
+              } else {
+                e0 = ex2_approx(fmaf(a, sl2, neg_ms));
+                e1 = ex2_approx(fmaf(b2v, sl2, neg_ms));
+              }
+              sm[(c >> 1) & 3] += e0 + e1;
+              p[8 * k + (c >> 1)] = pack_bf16x2_rn(e0, e1);
+            }
+          }
+        }
+        tile_max = fmaxf(mx[0], mx[1]);
+        tile_sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
+      };
+      // Steady state: exponentiate against the running max of the previous steps; only
+      // when some score of the row group lies more than 2^8 above it (always on the first
+      // step) do both threads of each row exchange maxima, rescale and redo the pass.
+      bool mine;
+      if (j != 0) {
+        pass(true);
+        mine = __any_sync(0xffffffffu, (tile_max - row_max) * sl2 > 8.0f);
+      } else {
+        pass(false);
+        mine = true;
+      }
+      volatile int* flag = redo_flags + (j & 1) * 8 + t * 4 + quarter;
+      if (mine && lane == 0) *flag = 1;
+      pair_sync();
+      if (*flag != 0) {
+        *my_x = tile_max;
+        pair_sync();
+        const float m_row = fmaxf(tile_max, *other_x);
         float alpha = 1.0f;
-        if (raise) {
-          alpha = ex2_approx((row_max - m) * sl2);  // 0 on the first step
-          row_max = m;
+        if ((m_row - row_max) * sl2 > 8.0f) {   // identical decision in both threads of the row
+          alpha = ex2_approx((row_max - m_row) * sl2);  // 0 on the first step
+          row_max = m_row;
           row_sum *= alpha;
         }
         if (j != 0) {
 #pragma unroll 1
-          for (int c = 0; c < HEAD_DIM; c += 32) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(o_tmem + c, o);
+          for (int c = 0; c < 64; c += 16) {
+            uint32_t o[16];
+            tmem_ld_32x32b_x16(o_tmem + c, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32b_x32(o_tmem + c, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x16(o_tmem + c, o);
           }
         }
+        pass(true);
+        pair_sync();   // both have read the flag and the exchanged maxima
+        if (half == 0 && lane == 0) *flag = 0;  // next used two steps later
       }
-      const float neg_ms = -row_max * sl2;
-      uint32_t p[64];
-      float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float e0 = ex2_approx(fmaf(__uint_as_float(sraw[2 * c]), sl2, neg_ms));
-        const float e1 = ex2_approx(fmaf(__uint_as_float(sraw[2 * c + 1]), sl2, neg_ms));
-        sum0 += e0;
-        sum1 += e1;
-        p[c] = pack_bf16x2_rn(e0, e1);
-      }
-      row_sum += sum0 + sum1;
+      row_sum += tile_sum;
       {
-        uint32_t(&p0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&p[0]);
-        uint32_t(&p1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&p[32]);
-        tmem_st_32x32b_x32(s_tmem + 0, p0);
-        tmem_st_32x32b_x32(s_tmem + 32, p1);
+        uint32_t(&p0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&p[0]);
+        uint32_t(&p1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&p[16]);
+        tmem_st_32x32b_x16(p_tmem + 0, p0);
+        tmem_st_32x32b_x16(p_tmem + 16, p1);
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(P_FULL + t));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + t));  // one arrival per warp, 8 per tile
     }
-    // ---- final: O / l -> bf16 -> global (BSHD) ----
+    // ---- final: O / l -> bf16 -> global (BSHD); l = both halves' sums ----
     if (ok) ok = mbar_wait(bar(O_FULL + t), 0, abort_flag, kStatusFlashTimeout);
+    *my_x = row_sum;
+    pair_sync();
     if (ok) {
       tc_fence_after();
-      const int row = (pair * 2 + t) * BLOCK_M + quarter * 32 + lane;
-      const float inv = (row_sum == 0.f || row_sum != row_sum) ? 1.0f : 1.0f / row_sum;
+      const float l = row_sum + *other_x;
+      const int row = (pair * 2 + t) * BLOCK_M + row_in_tile;
+      const float inv = (l == 0.f || l != l) ? 1.0f : 1.0f / l;
       __nv_bfloat16* dst =
-          args.out + (((int64_t)b * args.S + row) * args.H + h) * (int64_t)HEAD_DIM;
+          args.out + (((int64_t)b * args.S + row) * args.H + h) * (int64_t)HEAD_DIM + half * 64;
 #pragma unroll 1
-      for (int c = 0; c < HEAD_DIM; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         uint32_t o[32];
         tmem_ld_32x32b_x32(o_tmem + c, o);
         tmem_wait_ld();
@@ -331,7 +420,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }

@@ -26,8 +26,6 @@ static inline unsigned int read_and_clear_device_status() {
 constexpr unsigned int kStatusGemmTimeout = 0x1u;
 constexpr unsigned int kStatusFlashTimeout = 0x2u;
 
-// A wait gives up after this many SM clock cycles (about one second).
-constexpr long long kSpinLimitCycles = 2000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -69,21 +67,46 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait: returns false (after recording `code` and raising *abort_flag)
-// when the phase did not complete within kSpinLimitCycles or another role already
-// aborted.  Callers leave their loops and fall through to the common teardown.
+// Bounded wait: returns false (after recording `code` and raising *abort_flag) when the
+// phase did not complete within the poll budget or another role already aborted.  Callers
+// leave their loops and fall through to the common teardown.  The bound is a poll COUNT,
+// not a clock reading: special-register reads are slow when the SM's transcendental unit
+// is saturated, and these waits sit on the tensor pipe's critical path.
+constexpr uint32_t kWaitPollLimit = 1u << 26;   // suspending try_wait polls (>= ~1 s)
+constexpr uint32_t kSpinPollLimit = 1u << 27;   // non-suspending test_wait polls (~1-2 s)
+
+__device__ __forceinline__ bool mbar_give_up(volatile int* abort_flag, unsigned int code) {
+  atomicOr(&g_device_status, code);
+  *abort_flag = 1;
+  return false;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag != 0 || clock64() - start > kSpinLimitCycles) {
-      atomicOr(&g_device_status, code);
-      *abort_flag = 1;
-      return false;
-    }
+#pragma unroll 1
+  for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag != 0) break;
   }
-  return true;
+  return mbar_give_up(abort_flag, code);
+}
+// Low-latency variant for a single waiting thread: spins on the non-suspending
+// mbarrier.test_wait (try_wait may park the thread and wake it late).
+__device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag, unsigned int code) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < kSpinPollLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 1023u) == 1023u && *abort_flag != 0) break;
+  }
+  return mbar_give_up(abort_flag, code);
 }
 
 // ---- TMA (tiled bulk tensor loads, no multicast) ----------------------------------
@@ -157,6 +180,178 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// High word of a 128-byte-swizzle shared-memory descriptor with an 8-row-group stride of
+// 1024 bytes: SBO >> 4 = 64 (bits 32-45), version 1 (bits 46-47), swizzle code 2 (61-63).
+constexpr uint32_t kDescHiSw128 = 64u | (1u << 14) | (2u << 29);
+// Low word: start address >> 4 (bits 0-13) and the leading byte offset >> 4 (bits 16-29).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3fffu) | ((lbo_bytes >> 4) << 16);
+}
+
+// Eight back-to-back bf16 MMAs D[tmem] = A.B^T over a 128-wide K extent held as two
+// K-major 128-byte-swizzled half tiles (64 elements each, second half `half_step` 16-byte
+// units after the first): 32 bytes of K per MMA, the first MMA overwrites D.  One asm
+// block, so the issuing thread executes the minimum instruction stream.
+__device__ __forceinline__ void mma_f16_ss_k128(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                uint32_t idesc, uint32_t half_step) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 da, db;\n\t"
+      ".reg .b32 al, bl;\n\t"
+      "setp.ne.b32 p0, 0, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p0;\n\t"
+      "add.u32 al, %1, 2; add.u32 bl, %2, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, %1, 4; add.u32 bl, %2, 4; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, %1, 6; add.u32 bl, %2, 6; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, %1, %5; add.u32 bl, %2, %5; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, al, 2; add.u32 bl, bl, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, al, 2; add.u32 bl, bl, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, al, 2; add.u32 bl, bl, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(half_step)
+      : "memory");
+}
+
+// Eight back-to-back bf16 MMAs D[tmem] (+)= A[tmem].B with A read from tensor memory
+// (8 columns = 16 bf16 of K per MMA) and B an MN-major shared-memory operand advancing
+// `b_step` 16-byte units per MMA.  `accumulate` applies to the first MMA only.
+__device__ __forceinline__ void mma_f16_ts_step8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                              uint32_t idesc, uint32_t b_step,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 db;\n\t"
+      ".reg .b32 at, bl;\n\t"
+      "setp.ne.b32 p0, %6, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p0;\n\t"
+      "add.u32 at, %1, 8; add.u32 bl, %2, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(b_step), "r"(accumulate)
+      : "memory");
+}
+
+// Eight back-to-back bf16 MMAs from PRE-BUILT 64-bit descriptors: the issuing thread
+// executes one instruction per MMA, so it keeps the tensor pipe fed even when it has to
+// compete for issue slots with busy warps on its scheduler.  The first MMA overwrites D.
+__device__ __forceinline__ void mma_f16_ss_x8(uint32_t d_tmem, const uint64_t (&a)[8],
+                                              const uint64_t (&b)[8], uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, 0, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %9, %17, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %17, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]),
+      "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
+      "r"(idesc)
+      : "memory");
+}
+// Same with A read from tensor memory (addresses a[i]); `accumulate` applies to the first.
+__device__ __forceinline__ void mma_f16_ts_x8(uint32_t d_tmem, const uint32_t (&a)[8],
+                                              const uint64_t (&b)[8], uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %18, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %9, %17, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %10, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %11, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %17, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %17, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
+      "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
+      "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Eight back-to-back bf16 MMAs from tables of descriptor LOW words (the high word is the
+// same for every 128-byte-swizzle descriptor): three instructions per MMA and half the
+// registers of full 64-bit tables.  The first MMA overwrites D.
+#define B2_SS_LO(ai, bi, pred)                                                         \
+  "mov.b64 da, {%" #ai ", %17}; mov.b64 db, {%" #bi ", %17};\n\t"                     \
+  "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %18, " pred ";\n\t"
+__device__ __forceinline__ void mma_f16_ss_lo_x8(uint32_t d_tmem, const uint32_t (&a)[8],
+                                                 const uint32_t (&b)[8], uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p0, 0, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t" B2_SS_LO(1, 9, "p0") B2_SS_LO(2, 10, "p1") B2_SS_LO(3, 11, "p1")
+          B2_SS_LO(4, 12, "p1") B2_SS_LO(5, 13, "p1") B2_SS_LO(6, 14, "p1") B2_SS_LO(7, 15, "p1")
+              B2_SS_LO(8, 16, "p1") "}" ::"r"(d_tmem),
+      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
+      "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]),
+      "r"(kDescHiSw128), "r"(idesc)
+      : "memory");
+}
+#undef B2_SS_LO
+// Same with A read from tensor memory (addresses a[i]); `accumulate` applies to the first.
+#define B2_TS_LO(ai, bi, pred)                    \
+  "mov.b64 db, {%" #bi ", %17};\n\t"             \
+  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%" #ai "], db, %18, " pred ";\n\t"
+__device__ __forceinline__ void mma_f16_ts_lo_x8(uint32_t d_tmem, const uint32_t (&a)[8],
+                                                 const uint32_t (&b)[8], uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p0, %19, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t" B2_TS_LO(1, 9, "p0") B2_TS_LO(2, 10, "p1") B2_TS_LO(3, 11, "p1")
+          B2_TS_LO(4, 12, "p1") B2_TS_LO(5, 13, "p1") B2_TS_LO(6, 14, "p1") B2_TS_LO(7, 15, "p1")
+              B2_TS_LO(8, 16, "p1") "}" ::"r"(d_tmem),
+      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
+      "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]),
+      "r"(kDescHiSw128), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+#undef B2_TS_LO
+
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 __device__ __forceinline__ void tmem_wait_ld() {
