@@ -74,14 +74,17 @@ __device__ __forceinline__ float row_scale_from_absmax(float absmax, float* reci
   return scale;
 }
 
-// Quantise one packed pair with the row reciprocal: bf16(x*r) -> clamp -> round
-// half even -> low byte.  Returns the two int8 in bits 0-7 and 8-15.
+// Quantise one packed pair with the row reciprocal: bf16(x*r) -> clamp -> round half even
+// -> low byte.  Returns the two int8 in bits 0-7 and 8-15.
+// Only the upper clamp can ever act: |x| <= absmax and the divisor is bf16(absmax/127)
+// (or the 1e-30 floor), so |bf16(x*r)| <= 127.5, which rounds to +128 (clamped to 127) or
+// to -128 (in range).  Rows with a NaN or infinite divisor never get here (zero_row).
 __device__ __forceinline__ uint32_t quant_pair(uint32_t w, float r) {
   float d0 = __fmul_rn(bf16lo_to_f32(w), r);
   float d1 = __fmul_rn(bf16hi_to_f32(w), r);
   uint32_t p = pack_bf16x2_rn(d0, d1);
-  float e0 = fminf(fmaxf(bf16lo_to_f32(p), -128.0f), 127.0f);
-  float e1 = fminf(fmaxf(bf16hi_to_f32(p), -128.0f), 127.0f);
+  float e0 = fminf(bf16lo_to_f32(p), 127.0f);
+  float e1 = fminf(bf16hi_to_f32(p), 127.0f);
   // adding 1.5*2^23 rounds to nearest-even integer; the low mantissa byte is the
   // two's-complement int8
   uint32_t b0 = __float_as_uint(__fadd_rn(e0, 12582912.0f));

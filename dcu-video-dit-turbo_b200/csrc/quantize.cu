@@ -113,12 +113,48 @@ __global__ void fill_f32_kernel(float* p, int64_t n, float v) {
 
 // ---- SwiGLU + quantizer ------------------------------------------------------
 
-// bf16( bf16(g / (1 + expf(-g))) * u ) on a packed pair; fp32 math, IEEE divide,
-// the accurate expf (no fast-math), two bf16 roundings.
+// SiLU in fp32 exactly as the eager op computes it: g / (1 + expf(-g)) with the accurate
+// expf and an IEEE division.
+__device__ __forceinline__ float silu_exact(float g) {
+  return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+}
+// Fast SiLU: ex2.approx and rcp.approx instead of expf and the division.  Only its
+// ROUNDING TO BF16 has to equal the exact one's.  The exponent argument g*log2(e) is
+// carried as a rounded product plus its exact residual (two FMAs on the otherwise idle FMA
+// pipe), which keeps the relative error of the fast result within a few fp32 ulps for
+// |g| <= 64; whenever the fast fp32 result lies more than 16 ulps away from a bf16 rounding
+// midpoint (low 16 bits == 0x8000) both versions therefore round to the same bf16.
+// Otherwise *sure is cleared and the caller recomputes exactly (0.05 % of the elements).
+// tests/test_gpu_int8_path.py checks the result against the eager op for all 65536 gates.
+__device__ __forceinline__ float silu_fast(float g, bool* sure) {
+  constexpr float kNegLog2eHi = -1.4426950216293335f;   // fp32(log2 e), negated
+  constexpr float kNegLog2eLo = -1.9259629911266175e-8f;  // log2 e - fp32(log2 e), negated
+  const float t = g * kNegLog2eHi;
+  float r = fmaf(g, kNegLog2eHi, -t);  // exact rounding residual of the product
+  r = fmaf(g, kNegLog2eLo, r);
+  float e, rc;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+  e = fmaf(e, r * 0.6931471805599453f, e);  // 2^(t+r) = 2^t * (1 + r ln 2)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + e));
+  const float s = g * rc;
+  // |g| <= 64 keeps every intermediate finite and normal (beyond it: exact path)
+  *sure = (fabsf(g) <= 64.0f) && (((__float_as_uint(s) & 0xffffu) - (0x8000u - 16u)) > 32u);
+  return s;
+}
+
+// bf16( bf16(silu(g)) * u ) on a packed pair; two bf16 roundings.
 __device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
   const float g0 = bf16lo_to_f32(g), g1 = bf16hi_to_f32(g);
-  const float s0 = __fdiv_rn(g0, __fadd_rn(1.0f, expf(-g0)));
-  const float s1 = __fdiv_rn(g1, __fadd_rn(1.0f, expf(-g1)));
+  bool sure0, sure1;
+  float s0 = silu_fast(g0, &sure0);
+  float s1 = silu_fast(g1, &sure1);
+  // A vote over the lanes that are converged here keeps the rare exact path a real branch
+  // instead of predicated code.  The mask must be the ACTIVE mask: the scalar fallback
+  // kernel calls this from loops whose trip count differs between lanes.
+  if (__any_sync(__activemask(), !(sure0 && sure1))) {
+    s0 = silu_exact(g0);
+    s1 = silu_exact(g1);
+  }
   const uint32_t s = pack_bf16x2_rn(s0, s1);
   return pack_bf16x2_rn(__fmul_rn(bf16lo_to_f32(s), bf16lo_to_f32(u)),
                         __fmul_rn(bf16hi_to_f32(s), bf16hi_to_f32(u)));

@@ -152,6 +152,28 @@ def test_swiglu_quant(cuda_pkg, ref, m, k):
         assert float((diff != 0).float().mean()) <= 1e-4 + 1.0 / diff.numel(), name
 
 
+def test_swiglu_all_65536_gate_values(cuda_pkg):
+    """SiLU -> bf16 is a function of the bf16 gate alone, so it can be checked exhaustively.
+    Row r holds gate pattern r (8 copies) and up = 1: the row scale is then
+    |bf16(silu(g))| * fp32(1/127), which is injective in the bf16 value, and q carries
+    its sign.  Equality with the eager op on the same device for every row proves the
+    kernel's SiLU (including its fast path and boundary fallback) for all 65536 gates;
+    a second pass with up = 3 exercises the second rounding."""
+    gates = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    for up_value in (1.0, 3.0):
+        x = torch.empty((65536, 16), dtype=torch.bfloat16)
+        x[:, :8] = gates[:, None]
+        x[:, 8:] = up_value
+        xd = x.to(DEV)
+        q, s = cuda_pkg.ops.swiglu_quantize_int8_rowwise(xd)
+        qd, sd = _torch_device_swiglu_quant(xd)
+        nan = torch.isnan(sd.view(-1))
+        assert torch.equal(torch.isnan(s.view(-1)), nan)
+        assert torch.equal(bits(s.view(-1))[~nan], bits(sd.view(-1))[~nan]), \
+            f"{(bits(s.view(-1))[~nan] != bits(sd.view(-1))[~nan]).sum().item()} gate values differ"
+        assert torch.equal(q, qd)
+
+
 def test_swiglu_config3b_rows(cuda_pkg, ref):
     g = torch.Generator().manual_seed(20260813)
     x = torch.randn((512, 16384), generator=g).to(torch.bfloat16)
