@@ -27,12 +27,17 @@ int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* 
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
                      const float* rs, const float* cs, const void* bias, int bias_kind, int64_t M,
                      int64_t N, int64_t K, cudaStream_t stream);
+// CTA-pair (cta_group::2) variant; returns -1 when it does not apply.
+int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
+                          const float* rs, const float* cs, const void* bias, int bias_kind,
+                          int64_t M, int64_t N, int64_t K, cudaStream_t stream);
 int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
                      cudaStream_t stream);
 
 // Read and clear the device-side status word of a tensor-core translation unit.
 unsigned int read_clear_status_gemm();
+unsigned int read_clear_status_gemm2();
 unsigned int read_clear_status_flash();
 
 }  // namespace b2

@@ -292,6 +292,9 @@ int encode_k_major_map(CUtensorMap* map, const void* base, int64_t rows, int64_t
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
                      const float* rs, const float* cs, const void* bias, int bias_kind, int64_t M,
                      int64_t N, int64_t K, cudaStream_t stream) {
+  // large M: two CTAs per 256x256 tile (less operand traffic per SM); else one CTA per tile
+  const int pair_status = launch_int8_gemm_pair(A, W, out_i32, out_bf16, rs, cs, bias, bias_kind, M, N, K, stream);
+  if (pair_status >= 0) return pair_status;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(int8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
