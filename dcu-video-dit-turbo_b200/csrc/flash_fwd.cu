@@ -24,11 +24,12 @@
 //     warps 10-17  the same for query tile 1
 //   The two tiles ping-pong: while one tile's softmax runs, the tensor core works on
 //   the other tile's MMAs.  P overwrites S in place as bf16.
-//   Softmax runs against the running row max of the PREVIOUS steps, so the max is off
-//   the critical path; the running max is only raised (and O, l rescaled, P recomputed)
-//   when a new score exceeds it by more than 2^8 in the exp2 domain, which after the
-//   first steps almost never happens.  The two threads of a row agree on that through a
-//   shared-memory flag and a two-warp mbarrier handshake per step; the final O/l is exact.
+//   Per step a thread loads its 64 scores, the two threads of a row exchange their maxima
+//   (shared memory + a 64-thread named barrier) and raise the running max, rescaling O
+//   and l, only when it lags by more than 2^8 in the exp2 domain (rare after the first
+//   steps; the final O/l is exact either way).  P is published in two column halves, each
+//   with its own mbarrier, so the tensor core starts O += P.V on the first half while the
+//   second half is still being exponentiated.
 // Every mbarrier wait is bounded; on a timeout the kernel records a status word and
 // returns through the common teardown.
 #include <cmath>
@@ -62,13 +63,13 @@ constexpr int SMEM_Q = 0;                                   // 2 tiles
 constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;             // KV_STAGES tiles
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;     // KV_STAGES tiles
 constexpr int SMEM_BARS = SMEM_V + KV_STAGES * TILE_BYTES;  // 16 mbarriers + tmem slot + abort
-constexpr int NUM_BARS = 24;
-constexpr int SMEM_XCHG = SMEM_BARS + NUM_BARS * 8 + 16;    // flags [2][8] + row exchange [2][2][128]
-constexpr int SMEM_TOTAL = 1024 + SMEM_XCHG + 2 * 8 * 4 + 2 * 2 * 128 * 4;
+constexpr int NUM_BARS = 18;
+constexpr int SMEM_XCHG = SMEM_BARS + NUM_BARS * 8 + 16;    // row exchange floats [2 tiles][2 halves][128 rows]
+constexpr int SMEM_TOTAL = 1024 + SMEM_XCHG + 2 * 2 * 128 * 4;
 
 // mbarrier indices
 enum { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_FULL = 12,
-       O_FULL = 14, PAIR_SYNC = 16 /* 8: one per (tile, lane quarter) */ };
+       O_FULL = 14, PB_FULL = 16 /* second column half of P, per tile */ };
 
 struct FlashArgs {
   __nv_bfloat16* out;  // [B, S, H, 128]
@@ -141,8 +142,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* redo_flags = reinterpret_cast<volatile int*>(smem + SMEM_XCHG);  // [2][8]
-  volatile float* xchg = reinterpret_cast<volatile float*>(smem + SMEM_XCHG + 2 * 8 * 4);  // [2][2][128]
+  volatile float* xchg = reinterpret_cast<volatile float*>(smem + SMEM_XCHG);  // [2][2][128]
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int idx) -> uint32_t { return bar0 + idx * 8; };
@@ -154,14 +154,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i)
-      mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 8 : (i >= PAIR_SYNC ? 2 : 1));
+      mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1 || i >= PB_FULL) ? 8 : 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  if (threadIdx.x < 16) redo_flags[threadIdx.x] = 0;
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -201,12 +200,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       build_kmajor_lo(q1, sbase + SMEM_Q + TILE_BYTES);
       build_kmajor_lo(kA, sbase + SMEM_K);
       build_kmajor_lo(kB, sbase + SMEM_K + TILE_BYTES);
-      build_v_lo(vA, sbase + SMEM_V);
-      build_v_lo(vB, sbase + SMEM_V + TILE_BYTES);
+      // P.V tables in PUBLICATION order: the first column half of P covers kv rows
+      // [0,32) and [64,96) (MMAs 0,1,4,5 of the natural order), the second the rest.
+      {
+        uint32_t va[8], vb[8];
+        build_v_lo(va, sbase + SMEM_V);
+        build_v_lo(vb, sbase + SMEM_V + TILE_BYTES);
+        constexpr int order[8] = {0, 1, 4, 5, 2, 3, 6, 7};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        pa0[i] = s0 + i * 8;  // P: 8 tensor-memory columns (16 bf16 of kv) per MMA
-        pa1[i] = s1 + i * 8;
+        for (int i = 0; i < 8; ++i) {
+          vA[i] = va[order[i]];
+          vB[i] = vb[order[i]];
+          pa0[i] = s0 + order[i] * 8;  // P: 8 tensor-memory columns (16 bf16 of kv) per MMA
+          pa1[i] = s1 + order[i] * 8;
+        }
       }
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, kStatusFlashTimeout) &&
                 mbar_wait(bar(K_FULL), 0, abort_flag, kStatusFlashTimeout);
@@ -231,7 +238,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
         if (!mbar_wait(bar(P_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        mma_f16_ts_lo_x8(o0, pa0, vd, kIdescPV, j != 0);
+        mma_f16_ts_lo_x4(o0, pa0, vd, kIdescPV, j != 0);
+        if (!mbar_wait(bar(PB_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
+        tc_fence_after();
+        mma_f16_ts_lo_x4(o0, pa0 + 4, vd + 4, kIdescPV, 1);
         if (last) {
           tc_commit(bar(O_FULL));
         } else {
@@ -242,7 +252,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         if (!mbar_wait(bar(P_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        mma_f16_ts_lo_x8(o1, pa1, vd, kIdescPV, j != 0);
+        mma_f16_ts_lo_x4(o1, pa1, vd, kIdescPV, j != 0);
+        if (!mbar_wait(bar(PB_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
+        tc_fence_after();
+        mma_f16_ts_lo_x4(o1, pa1 + 4, vd + 4, kIdescPV, 1);
         tc_commit(bar(V_EMPTY + st));
         if (last) {
           tc_commit(bar(O_FULL + 1));
@@ -271,9 +284,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t o_tmem = tmem_base + (t ? COL_O1 : COL_O0) + lane_sel + half * 64;
     // The two warps that share a row group meet at a named barrier (bar.sync id, 64).
     // bar.sync has no time limit, so the loop below never leaves early: after an abort a
-    // warp keeps walking the remaining steps, skips the waits and the arithmetic, and
-    // still executes every barrier its partner will execute (the count per step depends
-    // only on a flag both read after the first barrier).
+    // warp keeps walking the remaining steps, skips the mbarrier waits, and still executes
+    // the one barrier per step (and the one after the loop) that its partner executes.
     const uint32_t pair_bar = 1 + t * 4 + quarter;
     bool ok = true;
     auto pair_sync = [&]() { named_barrier_sync(pair_bar, 64); };
@@ -281,104 +293,86 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     volatile float* other_x = xchg + (t * 2 + (half ^ 1)) * 128 + row_in_tile;
     const float sl2 = args.scale_log2;
     const int tail_valid = args.S - (n_kv - 1) * BLOCK_N;  // valid columns of the last step
-    float row_max = -INFINITY;  // raw-score domain, shared by both threads of the row
+    float row_max = -INFINITY;  // raw-score domain, identical in both threads of the row
     float row_sum = 0.f;        // this thread's 64 columns only
     for (int j = 0; j < n_kv; ++j) {
       if (ok) ok = mbar_wait(bar(S_FULL + t), j & 1, abort_flag, kStatusFlashTimeout);
       tc_fence_after();
+      // this thread's 64 scores -> registers
+      uint32_t s[64];
+      {
+        uint32_t(&c0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[0]);
+        uint32_t(&c1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[16]);
+        uint32_t(&c2)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[32]);
+        uint32_t(&c3)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[48]);
+        tmem_ld_32x32b_x16(s_tmem + 0, c0);
+        tmem_ld_32x32b_x16(s_tmem + 16, c1);
+        tmem_ld_32x32b_x16(s_tmem + 32, c2);
+        tmem_ld_32x32b_x16(s_tmem + 48, c3);
+        tmem_wait_ld();
+      }
       // columns of this thread that are valid in this step (tail masking)
       const int valid = ((j + 1 == n_kv) ? tail_valid : BLOCK_N) - half * 64;
-      uint32_t p[32];
-      float tile_max, tile_sum;
-      // One pass over this thread's 64 S columns in four 16-column chunks, double buffered
-      // so the tensor-memory load of chunk k+1 overlaps the arithmetic of chunk k.
-      auto pass = [&](const bool do_exp) {
-        const float neg_ms = -row_max * sl2;
-        float mx[2] = {-INFINITY, -INFINITY};
-        float sm[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t buf[2][16];
-        tmem_ld_32x32b_x16(s_tmem, buf[0]);
+      if (valid < 64) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          tmem_wait_ld();
-          if (k < 3) tmem_ld_32x32b_x16(s_tmem + 16 * (k + 1), buf[(k + 1) & 1]);
-          uint32_t(&v)[16] = buf[k & 1];
-          if (valid < 16 * (k + 1)) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-              if (16 * k + c >= valid) v[c] = 0xff800000u;  // -inf
-          }
-#pragma unroll
-          for (int c = 0; c < 16; c += 2) {
-            const float a = __uint_as_float(v[c]), b2v = __uint_as_float(v[c + 1]);
-            mx[(c >> 1) & 1] = fmax3(mx[(c >> 1) & 1], a, b2v);
-            if (do_exp) {
-              float e0, e1;
-              if (kPolyEvery != 0 && ((c >> 1) % (kPolyEvery ? kPolyEvery : 1)) == 0) {
-                e0 = ex2_poly(fmaf(a, sl2, neg_ms));  // this pair's exp2 on the FMA pipe
-                e1 = ex2_poly(fmaf(b2v, sl2, neg_ms));
-              } else {
-                e0 = ex2_approx(fmaf(a, sl2, neg_ms));
-                e1 = ex2_approx(fmaf(b2v, sl2, neg_ms));
-              }
-              sm[(c >> 1) & 3] += e0 + e1;
-              p[8 * k + (c >> 1)] = pack_bf16x2_rn(e0, e1);
-            }
-          }
-        }
-        tile_max = fmaxf(mx[0], mx[1]);
-        tile_sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
-      };
-      // Steady state: exponentiate against the running max of the previous steps; only
-      // when some score of the row group lies more than 2^8 above it (always on the first
-      // step) do both threads of each row exchange maxima, rescale and redo the pass.
-      bool mine;
-      if (j != 0) {
-        pass(true);
-        mine = __any_sync(0xffffffffu, (tile_max - row_max) * sl2 > 8.0f);
-      } else {
-        pass(false);
-        mine = true;
+        for (int c = 0; c < 64; ++c)
+          if (c >= valid) s[c] = 0xff800000u;  // -inf
       }
-      volatile int* flag = redo_flags + (j & 1) * 8 + t * 4 + quarter;
-      if (mine && lane == 0) *flag = 1;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; c += 2)
+        mx[(c >> 1) & 3] = fmax3(mx[(c >> 1) & 3], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+      const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // the row's max over all 128 columns: exchange with the partner thread.  After the
+      // barrier both threads have also finished READING S, so P may overwrite it.
+      *my_x = my_max;
       pair_sync();
-      if (*flag != 0) {
-        *my_x = tile_max;
-        pair_sync();
-        const float m_row = fmaxf(tile_max, *other_x);
-        float alpha = 1.0f;
-        if ((m_row - row_max) * sl2 > 8.0f) {   // identical decision in both threads of the row
-          alpha = ex2_approx((row_max - m_row) * sl2);  // 0 on the first step
-          row_max = m_row;
-          row_sum *= alpha;
-        }
-        if (j != 0) {
+      const float m_row = fmaxf(my_max, *other_x);
+      // lazy raise: identical decision in both threads of the row (true on the first step)
+      const bool raise = (m_row - row_max) * sl2 > 8.0f;
+      float alpha = 1.0f;
+      if (raise) {
+        alpha = ex2_approx((row_max - m_row) * sl2);  // 0 on the first step
+        row_max = m_row;
+        row_sum *= alpha;
+      }
+      if (j != 0 && __any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-          for (int c = 0; c < 64; c += 16) {
-            uint32_t o[16];
-            tmem_ld_32x32b_x16(o_tmem + c, o);
-            tmem_wait_ld();
+        for (int c = 0; c < 64; c += 16) {
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(o_tmem + c, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32b_x16(o_tmem + c, o);
-          }
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x16(o_tmem + c, o);
         }
-        pass(true);
-        pair_sync();   // both have read the flag and the exchanged maxima
-        if (half == 0 && lane == 0) *flag = 0;  // next used two steps later
       }
-      row_sum += tile_sum;
-      {
-        uint32_t(&p0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&p[0]);
-        uint32_t(&p1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&p[16]);
-        tmem_st_32x32b_x16(p_tmem + 0, p0);
-        tmem_st_32x32b_x16(p_tmem + 16, p1);
+      const float neg_ms = -row_max * sl2;
+      float sm[4] = {0.f, 0.f, 0.f, 0.f};
+      // two column halves of 32 scores, each published as soon as it is written
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t p[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float e0, e1;
+          if (kPolyEvery != 0 && ((c >> 1) % (kPolyEvery ? kPolyEvery : 1)) == 0) {
+            e0 = ex2_poly(fmaf(__uint_as_float(s[32 * hh + c]), sl2, neg_ms));
+            e1 = ex2_poly(fmaf(__uint_as_float(s[32 * hh + c + 1]), sl2, neg_ms));
+          } else {
+            e0 = ex2_approx(fmaf(__uint_as_float(s[32 * hh + c]), sl2, neg_ms));
+            e1 = ex2_approx(fmaf(__uint_as_float(s[32 * hh + c + 1]), sl2, neg_ms));
+          }
+          sm[(c >> 1) & 3] += e0 + e1;
+          p[c >> 1] = pack_bf16x2_rn(e0, e1);
+        }
+        tmem_st_32x32b_x16(p_tmem + 16 * hh, p);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar((hh ? PB_FULL : P_FULL) + t));  // one arrival per warp, 8 per tile
       }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL + t));  // one arrival per warp, 8 per tile
+      row_sum += (sm[0] + sm[1]) + (sm[2] + sm[3]);
     }
     // ---- final: O / l -> bf16 -> global (BSHD); l = both halves' sums ----
     if (ok) ok = mbar_wait(bar(O_FULL + t), 0, abort_flag, kStatusFlashTimeout);

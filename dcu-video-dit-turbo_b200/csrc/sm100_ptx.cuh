@@ -348,6 +348,29 @@ __device__ __forceinline__ void mma_f16_ts_lo_x8(uint32_t d_tmem, const uint32_t
       "r"(kDescHiSw128), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four MMAs, same conventions: a[0..3] tensor-memory A addresses, b[0..3] descriptor low words.
+__device__ __forceinline__ void mma_f16_ts_lo_x4(uint32_t d_tmem, const uint32_t* a,
+                                                 const uint32_t* b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p0, %11, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b64 db, {%5, %9};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %10, p0;\n\t"
+      "mov.b64 db, {%6, %9};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], db, %10, p1;\n\t"
+      "mov.b64 db, {%7, %9};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], db, %10, p1;\n\t"
+      "mov.b64 db, {%8, %9};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], db, %10, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]),
+      "r"(kDescHiSw128), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 #undef B2_TS_LO
 
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
