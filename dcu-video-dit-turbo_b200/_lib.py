@@ -25,6 +25,7 @@ SYMBOLS = {
     "b2_last_error": (ctypes.c_char_p, []),
     "b2_status_string": (ctypes.c_char_p, [_int]),
     "b2_check_device_status": (_int, [_vp]),
+    "b2_selftest_bounded_wait": (_int, [_vp]),
     "b2_quantize_int8_rowwise": (_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "b2_epilogue": (_int, [_vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _vp]),
     "b2_epilogue_vec4": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),

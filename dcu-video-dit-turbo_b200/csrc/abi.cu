@@ -72,6 +72,10 @@ int b2_check_device_status(void* stream) {
   return B2_OK;
 }
 
+int b2_selftest_bounded_wait(void* stream) {
+  return launch_bounded_wait_selftest((cudaStream_t)stream);
+}
+
 int b2_quantize_int8_rowwise(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                              void* stream) {
   if (M < 0 || K < 0) return fail(B2_BAD_SHAPE, "quantize: negative size M=%lld K=%lld", (long long)M, (long long)K);

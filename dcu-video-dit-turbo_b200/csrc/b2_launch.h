@@ -35,6 +35,7 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
                      cudaStream_t stream);
 
+int launch_bounded_wait_selftest(cudaStream_t stream);
 // Read and clear the device-side status word of a tensor-core translation unit.
 unsigned int read_clear_status_gemm();
 unsigned int read_clear_status_gemm2();

@@ -420,6 +420,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
 }
 
+// Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that nobody ever
+// arrives on, with a deliberately tiny poll budget.  The wait gives up, records the
+// status word and the kernel returns normally; the GPU context stays usable.
+__global__ void bounded_wait_selftest_kernel() {
+  __shared__ uint64_t never;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&never), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    bool done = false;
+    for (uint32_t i = 0; i < 4096u && !done; ++i) done = mbar_try_wait(smem_u32(&never), 0) != 0;
+    if (!done) mbar_give_up(&abort_flag, kStatusSelfTest);
+  }
+  __syncthreads();
+}
+
 // 4-D bf16 map over a logical [B,H,S,128] tensor; the two middle dimensions are
 // ordered by stride (ascending).  *swap = 1 when the order is (D, H, S, B).
 int encode_qkv_map(CUtensorMap* map, const void* base, int B, int H, int S, const int64_t* st,
@@ -457,6 +477,11 @@ int encode_qkv_map(CUtensorMap* map, const void* base, int B, int H, int S, cons
 }
 
 }  // namespace
+
+int launch_bounded_wait_selftest(cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>();
+  return check_launch("bounded_wait_selftest");
+}
 
 int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,

@@ -25,6 +25,7 @@ static inline unsigned int read_and_clear_device_status() {
 // Codes OR-ed into g_device_status by waits that gave up.
 constexpr unsigned int kStatusGemmTimeout = 0x1u;
 constexpr unsigned int kStatusFlashTimeout = 0x2u;
+constexpr unsigned int kStatusSelfTest = 0x100u;
 
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -52,6 +52,12 @@ const char* b2_status_string(int status);
  * clears it.  Synchronises `stream`.  Returns B2_OK or B2_TIMEOUT. */
 int b2_check_device_status(void* stream);
 
+/* Failure-detection self-test: launches one CTA whose only wait can never be satisfied
+ * and has a tiny poll budget.  The kernel gives up, records a status word and returns;
+ * the next b2_check_device_status() reports B2_TIMEOUT and clears it.  Nothing traps,
+ * faults or hangs.  (No counterpart in the reference, which has no device-side waits.) */
+int b2_selftest_bounded_wait(void* stream);
+
 /* Rowwise bf16 -> int8 quantizer.
  * Replaces h3_quantize_int8_rowwise_hip, kernels/exact-rowwise-int8/quantizer_kernel.hip:118-144
  * (Python: quantize_int8_rowwise(x) -> [q, scale], kernels/exact-rowwise-int8/quantizer.cpp:5-9).

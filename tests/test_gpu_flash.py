@@ -70,6 +70,18 @@ def test_small_gate(cuda_pkg, ref, seq, layout):
     assert torch.equal(out, out2)                                   # deterministic
 
 
+@pytest.mark.parametrize("batch,heads,seq", [(2, 3, 200), (3, 1, 129), (1, 1, 64)])
+def test_batches_and_single_head(cuda_pkg, ref, batch, heads, seq):
+    g = torch.Generator().manual_seed(batch * 100 + heads * 10 + seq)
+    q, k, v = (torch.randn(batch, heads, seq, 128, generator=g).to(torch.bfloat16) for _ in range(3))
+    want = ref.attention_fp32(q, k, v, 128 ** -0.5)
+    out = cuda_pkg.ops.fwd_bhsd(q.to(DEV), k.to(DEV), v.to(DEV), 128 ** -0.5)
+    cuda_pkg.ops.check_device_status()
+    assert out.shape == (batch, heads, seq, 128) and out.transpose(1, 2).is_contiguous()
+    bound = max(ENVELOPE, float(want.abs().max()) * 2 ** -7)
+    assert float((out.float().cpu() - want).abs().max()) <= bound
+
+
 def test_golden_fixture_from_reference_fp32(cuda_pkg):
     z = np.load(GOLD / "attention_fp32.npz")
     for idx in range(2):
@@ -165,3 +177,19 @@ def test_gated_attention_entry(cuda_pkg):
     assert pkg.attention.attention(q, k, v, H, skip_reshape=False, gates=g, sp_context=sp) == "host"
     assert g.dump_counters()["flash"]["reasons"] == {"mask": 1, "skip_reshape": 1}
     assert len(g.flash_fallback_signatures) == 2
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(cuda_pkg):
+    """Failure detection without a fault: a wait that can never complete runs out of its
+    poll budget, the host reads B2_TIMEOUT, the status clears, and the device still works."""
+    lib = cuda_pkg._lib.load()
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    assert lib.b2_check_device_status(stream) == 0
+    assert lib.b2_selftest_bounded_wait(stream) == 0
+    assert lib.b2_check_device_status(stream) == 6          # B2_TIMEOUT
+    assert b"bounded wait gave up" in lib.b2_last_error()
+    assert lib.b2_check_device_status(stream) == 0          # cleared
+    q = torch.randn(1, 2, 200, 128, device=DEV).to(torch.bfloat16)
+    out = cuda_pkg.ops.fwd_bhsd(q, q, q, 128 ** -0.5)
+    assert torch.isfinite(out.float()).all()
+    cuda_pkg.ops.check_device_status()

@@ -190,6 +190,7 @@ def _rand_i8(shape, g):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (1, 8, 16), (129, 264, 144), (100, 512, 3072),
+                                   (256, 8, 16), (300, 264, 144), (513, 520, 272), (1000, 256, 4096),
                                    (300, 3072, 3072), (257, 9216, 512), (640, 16384, 256),
                                    (77, 3072, 8192), (4096, 3072, 3072)])
 def test_int8_gemm_exact(cuda_pkg, ref, m, n, k):
@@ -208,6 +209,7 @@ def test_int8_gemm_exact(cuda_pkg, ref, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (5, 8, 16), (129, 264, 144), (300, 3072, 3072),
+                                   (257, 264, 144), (770, 520, 400),
                                    (4096, 3072, 3072), (333, 16384, 3072), (200, 3072, 8192)])
 def test_int8_gemm_fused_dequant_bit_exact(cuda_pkg, ref, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
