@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--head-chunks", type=int, default=0, help="0 = auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the 12 kernels one by one")
     ap.add_argument("--kernel", default=None,
                     choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant",
                              "epilogue", "gate", "rope"],
@@ -278,6 +279,14 @@ def run_b200(args):
         y = blk.forward(x_dev, cos, sin)
     ops.check_device_status(dev)
     attn_events.clear()
+    # single GPU: the pass is replayed from a CUDA graph (one launch instead of twelve);
+    # the attention events are recorded inside the captured pass by a second, eager run
+    use_graph = world == 1 and not args.no_graph
+    run_step = lambda xin: blk.forward(xin, cos, sin)
+    if use_graph:
+        blk._attn = orig_attn
+        graphed = pkg.block.GraphedBlock(blk, x_dev, cos, sin)
+        run_step = lambda xin: graphed.replay()      # input already resident in the captured buffer
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -287,11 +296,17 @@ def run_b200(args):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
-        y = blk.forward(x_dev, cos, sin)
+        y = run_step(x_dev)
     end.record()
     barrier()
     launches = ops.launch_count - launches0
     ms_step = max_over_ranks(start.elapsed_time(end) / args.steps)
+    if use_graph:
+        # attention kernel time inside a long step: same pass, eager, with events around it
+        blk._attn = timed_attn
+        for _ in range(args.steps):
+            blk.forward(x_dev, cos, sin)
+        torch.cuda.synchronize()
 
     attn_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in attn_events) / max(1, args.steps)
     attn_flops = sum(4.0 * s * s * h * HEAD_DIM for _, _, h, s in attn_events) / max(1, args.steps)
@@ -325,7 +340,9 @@ def run_b200(args):
             if i + 1 < n:
                 upload(i + 1)
             main.wait_event(up_done[i % 2])
-            y = blk.forward(x_bufs[i % 2], cos, sin)
+            # graph replays write one captured output buffer: clone it so that the download of
+            # step i can overlap the replay of step i+1
+            y = graphed(x_bufs[i % 2]).clone() if use_graph else blk.forward(x_bufs[i % 2], cos, sin)
             buf_free[i % 2].record(main)
             done = torch.cuda.Event()
             done.record(main)
@@ -385,7 +402,8 @@ def run_b200(args):
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8 GEMMs (s32 accumulate) + bf16 attention (f32 accumulate)",
             "data": "synthetic",
-            "config": workload_config(T, world, f"ulysses_sp{world}_headchunks{chunks}" if world > 1 else "single_gpu"),
+            "config": workload_config(T, world, f"ulysses_sp{world}_headchunks{chunks}" if world > 1
+                                      else ("single_gpu_cuda_graph" if use_graph else "single_gpu")),
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline,

@@ -57,3 +57,21 @@ def test_block_full_token_count_properties(cuda_pkg):
         parts.append(ops.int8_gemm_dequant(q8p, sp_.view(-1), p["wq_qkv"], p["ws_qkv"], p["b_qkv"]))
     assert torch.equal(full, torch.cat(parts))
     pkg.ops.check_device_status()
+
+
+def test_graphed_block_equals_eager_block(cuda_pkg):
+    pkg = cuda_pkg
+    T = 1500
+    params = pkg.block.make_block_params(seed=9, device=DEV)
+    cos, sin = pkg.block.rope_tables(pkg.block.grid_positions(T))
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    blk = pkg.block.DiTBlock(params)
+    x1 = torch.randn((T, 3072), device=DEV).to(torch.bfloat16)
+    x2 = torch.randn((T, 3072), device=DEV).to(torch.bfloat16)
+    graphed = pkg.block.GraphedBlock(blk, x1, cos, sin)
+    assert graphed.launches_per_replay == 12
+    for x in (x1, x2, x1):
+        want = blk.forward(x, cos, sin)
+        got = graphed(x).clone()
+        assert torch.equal(got, want)
+    pkg.ops.check_device_status()
