@@ -8,7 +8,8 @@ The reference project has no source for the block itself (it lives in the host
 application's model file); only its operator set comes from the reference.  The
 glue conventions (LayerNorm without affine, RMSNorm weight per head channel,
 rotary on adjacent pairs with three axis bands, bf16 gate vectors) are this
-package's own.  Twelve kernel launches per block on one GPU.
+package's own.  Ten kernel launches per block on one GPU (both gated residuals run in the
+epilogue of the GEMM that produces their operand).
 """
 from __future__ import annotations
 
@@ -102,19 +103,19 @@ class DiTBlock:
         qkv = qkv.view(L, 3, self.heads, self.head_dim)
         ops.qk_norm_rope_(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin)
         o = self.attention(qkv)
-        a = ops.int8_linear(o, p["wq_out"], p["ws_out"], p["b_out"])
-        ops.gate_residual_(x, a, p["gate1"])
+        q8, s = ops.quantize_int8_rowwise(o)
+        ops.int8_gemm_dequant_residual_(x, p["gate1"], q8, s.view(-1), p["wq_out"], p["ws_out"], p["b_out"])
         q8, s = ops.layernorm_mod_quant(x, p["scale2"], p["shift2"])
         f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])
-        f = ops.int8_linear(f, p["wq_fc2"], p["ws_fc2"], p["b_fc2"], input_act="swiglu")
-        ops.gate_residual_(x, f, p["gate2"])
+        q8, s = ops.swiglu_quantize_int8_rowwise(f)
+        ops.int8_gemm_dequant_residual_(x, p["gate2"], q8, s.view(-1), p["wq_fc2"], p["ws_fc2"], p["b_fc2"])
         return x
 
 
 class GraphedBlock:
     """One block pass captured in a CUDA graph (single GPU, fixed token count).
 
-    The twelve kernel launches of a pass replay as one graph launch, which removes the
+    The ten kernel launches of a pass replay as one graph launch, which removes the
     host-side launch gaps between them.  Shapes, weights and the rotary tables are
     fixed at capture time; `__call__` copies the input into the captured buffer, replays
     and returns the captured output buffer (overwritten by the next call).

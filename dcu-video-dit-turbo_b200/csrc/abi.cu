@@ -203,7 +203,7 @@ int b2_int8_gemm(const int8_t* A, const int8_t* W, int32_t* acc, int64_t M, int6
   int st = check_gemm("int8_gemm", A, W, M, N, K, 4);
   if (st >= 0) return st;
   if (!acc || !aligned16(acc)) return fail(B2_BAD_STRIDE, "int8_gemm: acc null or not 16-byte aligned");
-  return launch_int8_gemm(A, W, acc, nullptr, nullptr, nullptr, nullptr, B2_BIAS_NONE, M, N, K, (cudaStream_t)stream);
+  return launch_int8_gemm(A, W, acc, nullptr, nullptr, nullptr, nullptr, B2_BIAS_NONE, nullptr, nullptr, M, N, K, (cudaStream_t)stream);
 }
 
 int b2_int8_gemm_dequant(const int8_t* A, const float* rs, const int8_t* W, const float* cs,
@@ -215,7 +215,20 @@ int b2_int8_gemm_dequant(const int8_t* A, const float* rs, const int8_t* W, cons
   if (!rs || !cs || !out) return fail(B2_NULL_POINTER, "int8_gemm_dequant: null pointer");
   if (bias_kind != B2_BIAS_NONE && !bias) return fail(B2_NULL_POINTER, "int8_gemm_dequant: bias kind %d with a null bias", bias_kind);
   if (!aligned16(out)) return fail(B2_BAD_STRIDE, "int8_gemm_dequant: out must be 16-byte aligned");
-  return launch_int8_gemm(A, W, nullptr, out, rs, cs, bias, bias_kind, M, N, K, (cudaStream_t)stream);
+  return launch_int8_gemm(A, W, nullptr, out, rs, cs, bias, bias_kind, nullptr, nullptr, M, N, K, (cudaStream_t)stream);
+}
+
+int b2_int8_gemm_dequant_residual(const int8_t* A, const float* rs, const int8_t* W,
+                                  const float* cs, const void* bias, int bias_kind,
+                                  const void* gate, void* x_inout, int64_t M, int64_t N,
+                                  int64_t K, void* stream) {
+  if (bias_kind < B2_BIAS_NONE || bias_kind > B2_BIAS_FP32) return fail(B2_BAD_DTYPE, "int8_gemm_dequant_residual: bias must be none, bfloat16, or float32");
+  int st = check_gemm("int8_gemm_dequant_residual", A, W, M, N, K, 8);
+  if (st >= 0) return st;
+  if (!rs || !cs || !gate || !x_inout) return fail(B2_NULL_POINTER, "int8_gemm_dequant_residual: null pointer");
+  if (bias_kind != B2_BIAS_NONE && !bias) return fail(B2_NULL_POINTER, "int8_gemm_dequant_residual: bias kind %d with a null bias", bias_kind);
+  if (!aligned16(x_inout)) return fail(B2_BAD_STRIDE, "int8_gemm_dequant_residual: x must be 16-byte aligned");
+  return launch_int8_gemm(A, W, nullptr, nullptr, rs, cs, bias, bias_kind, gate, x_inout, M, N, K, (cudaStream_t)stream);
 }
 
 int b2_int8_linear(const void* x, int input_act, const int8_t* W, const float* cs, const void* bias,
@@ -232,7 +245,7 @@ int b2_int8_linear(const void* x, int input_act, const int8_t* W, const float* c
            ? launch_swiglu_quantize(x, q_scratch, s_scratch, M, K, (cudaStream_t)stream)
            : launch_quantize(x, q_scratch, s_scratch, M, K, (cudaStream_t)stream);
   if (st != B2_OK) return st;
-  return launch_int8_gemm(q_scratch, W, nullptr, out, s_scratch, cs, bias, bias_kind, M, N, K, (cudaStream_t)stream);
+  return launch_int8_gemm(q_scratch, W, nullptr, out, s_scratch, cs, bias, bias_kind, nullptr, nullptr, M, N, K, (cudaStream_t)stream);
 }
 
 int b2_flash_fwd(const void* q, const void* k, const void* v, void* out, int32_t B, int32_t H,

@@ -22,15 +22,17 @@ int launch_layernorm_mod(const void* x, const void* scale, const void* shift, vo
                          bool quant, cudaStream_t stream);
 int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* cos_tab,
                         const float* sin_tab, int64_t S, int H, float eps, cudaStream_t stream);
-// out_i32 != nullptr: plain int32 result.  Otherwise the fused dequant epilogue
-// writes bf16 to out_bf16.
+// out_i32 != nullptr: plain int32 result.  Otherwise the fused dequant epilogue writes
+// bf16 to out_bf16, or, with gate/residual non-null, x = bf16(x + bf16(gate*y)) in place.
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
-                     const float* rs, const float* cs, const void* bias, int bias_kind, int64_t M,
-                     int64_t N, int64_t K, cudaStream_t stream);
+                     const float* rs, const float* cs, const void* bias, int bias_kind,
+                     const void* gate, void* residual, int64_t M, int64_t N, int64_t K,
+                     cudaStream_t stream);
 // CTA-pair (cta_group::2) variant; returns -1 when it does not apply.
 int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
                           const float* rs, const float* cs, const void* bias, int bias_kind,
-                          int64_t M, int64_t N, int64_t K, cudaStream_t stream);
+                          const void* gate, void* residual, int64_t M, int64_t N, int64_t K,
+                          cudaStream_t stream);
 int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
                      cudaStream_t stream);

@@ -1,0 +1,99 @@
+// Epilogue shared by the single-CTA and the CTA-pair INT8 GEMM kernels: one thread owns
+// one accumulator row and walks it in 32-column chunks read from tensor memory.
+//
+//   plain      out_i32[row, col] = acc
+//   dequant    y = bf16( bf16(float(acc) * (rs[row]*cs[col])) + bf16(bias[col]) )
+//              (kernels/int8-epilogue/epilogue_kernel.hip:39-53 in the reference, bit-exact)
+//   residual   x[row, col] = bf16( x + bf16(gate[col] * y) ) in place: the gated residual
+//              of the DiT block applied while the tile is still in registers, so y never
+//              makes a round trip through memory
+#pragma once
+
+#include "b2_common.cuh"
+
+namespace b2 {
+
+struct EpilogueArgs {
+  int M, N;
+  int32_t* out_i32;            // plain mode when non-null
+  __nv_bfloat16* out_bf16;     // dequant mode
+  const float* rs;
+  const float* cs;
+  const void* bias;
+  int bias_kind;
+  const __nv_bfloat16* gate;   // residual mode when non-null (with `residual`)
+  __nv_bfloat16* residual;
+};
+
+constexpr int kEpiTileN = 256;
+constexpr int kColVecFloats = 3 * kEpiTileN;   // scale | bias | gate, per accumulator buffer
+
+// Stage the tile's per-column operands into shared memory (called by the 128 epilogue
+// threads, `et` in [0,128)); the caller synchronises them afterwards.
+__device__ __forceinline__ void epilogue_stage_columns(const EpilogueArgs& a, float* cvec, int col0,
+                                                       int et) {
+  for (int c = et; c < kEpiTileN; c += 128) {
+    const int col = col0 + c;
+    float s = 0.f, b = 0.f, g = 0.f;
+    if (col < a.N) {
+      s = a.cs[col];
+      if (a.bias_kind == B2_BIAS_BF16)
+        b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[col]);
+      else if (a.bias_kind == B2_BIAS_FP32)
+        b = round_bf16_f32(reinterpret_cast<const float*>(a.bias)[col]);
+      if (a.gate != nullptr) g = __bfloat162float(a.gate[col]);
+    }
+    cvec[c] = s;
+    cvec[kEpiTileN + c] = b;
+    cvec[2 * kEpiTileN + c] = g;
+  }
+}
+
+// One 32-column chunk of one row.  `c` is the chunk's offset inside the tile, `col` its
+// global column; the row is valid and col < N (checked by the caller).
+__device__ __forceinline__ void epilogue_store_chunk(const EpilogueArgs& a, const uint32_t (&v)[32],
+                                                     int row, int col, int c, float rsv,
+                                                     const float* cvec) {
+  if (a.out_i32 != nullptr) {
+    uint4* dst = reinterpret_cast<uint4*>(a.out_i32 + (int64_t)row * a.N + col);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)  // N % 4 == 0
+      if (col + j * 4 < a.N) dst[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    return;
+  }
+  const float* cscale = cvec + c;
+  const float* cbias = cvec + kEpiTileN + c;
+  const float* cgate = cvec + 2 * kEpiTileN + c;
+  const bool has_bias = a.bias_kind != B2_BIAS_NONE;
+  const bool residual = a.gate != nullptr;
+  __nv_bfloat16* base = (residual ? a.residual : a.out_bf16) + (int64_t)row * a.N + col;
+  uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) {  // N % 8 == 0: whole 8-column groups are in or out
+    if (col + j4 * 8 >= a.N) break;
+    uint32_t o[4];
+    uint4 xv = make_uint4(0, 0, 0, 0);
+    if (residual) xv = dst[j4];
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int j = j4 * 4 + jj;
+      const float f0 = __fmul_rn(__int2float_rn((int)v[2 * j]), __fmul_rn(rsv, cscale[2 * j]));
+      const float f1 = __fmul_rn(__int2float_rn((int)v[2 * j + 1]), __fmul_rn(rsv, cscale[2 * j + 1]));
+      uint32_t p = pack_bf16x2_rn(f0, f1);
+      if (has_bias)
+        p = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(p), cbias[2 * j]),
+                           __fadd_rn(bf16hi_to_f32(p), cbias[2 * j + 1]));
+      if (residual) {
+        const uint32_t g = pack_bf16x2_rn(__fmul_rn(bf16lo_to_f32(p), cgate[2 * j]),
+                                          __fmul_rn(bf16hi_to_f32(p), cgate[2 * j + 1]));
+        p = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(xw[jj]), bf16lo_to_f32(g)),
+                           __fadd_rn(bf16hi_to_f32(xw[jj]), bf16hi_to_f32(g)));
+      }
+      o[jj] = p;
+    }
+    dst[j4] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace b2

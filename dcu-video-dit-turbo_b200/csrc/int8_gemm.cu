@@ -21,6 +21,7 @@
 // drains and returns.
 #include "b2_common.cuh"
 #include "b2_launch.h"
+#include "gemm_epilogue.cuh"
 #include "sm100_ptx.cuh"
 
 namespace b2 {
@@ -56,19 +57,14 @@ constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 16;  // M-tiles swept per N pass (keeps the A group in L2)
 
 constexpr int SMEM_RING = STAGES * STAGE_BYTES;
-constexpr int SMEM_COLVEC = 2 * 2 * BN * 4;  // [buf][scale|bias][BN] fp32
+constexpr int SMEM_COLVEC = 2 * kColVecFloats * 4;  // [buf][scale|bias|gate][256] fp32
 constexpr int SMEM_BARS = 16 * 8;
 constexpr int SMEM_TOTAL = 1024 /*align slack*/ + SMEM_RING + SMEM_COLVEC + SMEM_BARS + 16;
 
 struct GemmArgs {
   int M, N, K;
   int tiles_m, tiles_n, num_tiles, k_blocks;
-  int32_t* out_i32;
-  __nv_bfloat16* out_bf16;
-  const float* rs;
-  const float* cs;
-  const void* bias;
-  int bias_kind;
+  EpilogueArgs epi;
 };
 
 __device__ __forceinline__ void decode_tile(int tile, const GemmArgs& a, int& m_idx, int& n_idx) {
@@ -187,67 +183,29 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int et = threadIdx.x - 64;
     int buf = 0;
     uint32_t buf_phase = 0;
-    const bool fused = args.out_i32 == nullptr;
+    const EpilogueArgs& epi = args.epi;
+    const bool fused = epi.out_i32 == nullptr;
     for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
       int m_idx, n_idx;
       decode_tile(tile, args, m_idx, n_idx);
       const int col0 = n_idx * BN;
-      float* cscale = colvec + buf * 2 * BN;
-      float* cbias = cscale + BN;
+      float* cvec = colvec + buf * kColVecFloats;
       if (fused) {
-        for (int c = et; c < BN; c += EPI_THREADS) {
-          const int col = col0 + c;
-          float s = 0.f, b = 0.f;
-          if (col < args.N) {
-            s = args.cs[col];
-            if (args.bias_kind == B2_BIAS_BF16)
-              b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col]);
-            else if (args.bias_kind == B2_BIAS_FP32)
-              b = round_bf16_f32(reinterpret_cast<const float*>(args.bias)[col]);
-          }
-          cscale[c] = s;
-          cbias[c] = b;
-        }
+        epilogue_stage_columns(epi, cvec, col0, et);
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
       if (!mbar_wait(tfull0 + buf * 8, buf_phase, abort_flag, kStatusGemmTimeout)) break;
       tc_fence_after();
       const int row = m_idx * BM + quarter * 32 + lane;
-      const bool row_ok = row < args.M;
-      const float rsv = (fused && row_ok) ? args.rs[row] : 0.f;
+      const bool row_ok = row < epi.M;
+      const float rsv = (fused && row_ok) ? epi.rs[row] : 0.f;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + c, v);
         tmem_wait_ld();
-        if (!row_ok || col0 + c >= args.N) continue;
-        if (fused) {
-          uint32_t o[16];
-          const bool has_bias = args.bias_kind != B2_BIAS_NONE;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float f0 = __fmul_rn(__int2float_rn((int)v[2 * j]), __fmul_rn(rsv, cscale[c + 2 * j]));
-            const float f1 =
-                __fmul_rn(__int2float_rn((int)v[2 * j + 1]), __fmul_rn(rsv, cscale[c + 2 * j + 1]));
-            uint32_t p = pack_bf16x2_rn(f0, f1);
-            if (has_bias)
-              p = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(p), cbias[c + 2 * j]),
-                                 __fadd_rn(bf16hi_to_f32(p), cbias[c + 2 * j + 1]));
-            o[j] = p;
-          }
-          uint4* dst = reinterpret_cast<uint4*>(args.out_bf16 + (int64_t)row * args.N + col0 + c);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)  // N % 8 == 0: whole 8-column groups are in or out
-            if (col0 + c + j * 8 < args.N)
-              dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-        } else {
-          uint4* dst = reinterpret_cast<uint4*>(args.out_i32 + (int64_t)row * args.N + col0 + c);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)  // N % 4 == 0
-            if (col0 + c + j * 4 < args.N)
-              dst[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        }
+        if (row_ok && col0 + c < epi.N) epilogue_store_chunk(epi, v, row, col0 + c, c, rsv, cvec);
       }
       tc_fence_before();
       __syncwarp();
@@ -290,10 +248,11 @@ int encode_k_major_map(CUtensorMap* map, const void* base, int64_t rows, int64_t
 }  // namespace
 
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
-                     const float* rs, const float* cs, const void* bias, int bias_kind, int64_t M,
-                     int64_t N, int64_t K, cudaStream_t stream) {
+                     const float* rs, const float* cs, const void* bias, int bias_kind,
+                     const void* gate, void* residual, int64_t M, int64_t N, int64_t K,
+                     cudaStream_t stream) {
   // large M: two CTAs per 256x256 tile (less operand traffic per SM); else one CTA per tile
-  const int pair_status = launch_int8_gemm_pair(A, W, out_i32, out_bf16, rs, cs, bias, bias_kind, M, N, K, stream);
+  const int pair_status = launch_int8_gemm_pair(A, W, out_i32, out_bf16, rs, cs, bias, bias_kind, gate, residual, M, N, K, stream);
   if (pair_status >= 0) return pair_status;
   static bool attr_set = false;
   if (!attr_set) {
@@ -318,12 +277,16 @@ int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* o
   if (tiles > 0x7fffffffLL) return fail(B2_TOO_LARGE, "int8_gemm: too many tiles");
   a.num_tiles = (int)tiles;
   a.k_blocks = (int)((K + BK - 1) / BK);
-  a.out_i32 = out_i32;
-  a.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out_bf16);
-  a.rs = rs;
-  a.cs = cs;
-  a.bias = bias;
-  a.bias_kind = bias_kind;
+  a.epi.M = (int)M;
+  a.epi.N = (int)N;
+  a.epi.out_i32 = out_i32;
+  a.epi.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  a.epi.rs = rs;
+  a.epi.cs = cs;
+  a.epi.bias = bias;
+  a.epi.bias_kind = bias_kind;
+  a.epi.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
+  a.epi.residual = reinterpret_cast<__nv_bfloat16*>(residual);
 
   int dev = 0, sms = kNumSMsB200;
   cudaGetDevice(&dev);

@@ -95,5 +95,5 @@ extern "C" int b2_int8_linear_noalloc(const void* x, int input_act, const int8_t
   st = input_act == B2_ACT_SWIGLU ? launch_swiglu_quantize(x, q_scratch, s_scratch, M, K, cs)
                                   : launch_quantize(x, q_scratch, s_scratch, M, K, cs);
   if (st != B2_OK) return st;
-  return launch_int8_gemm(q_scratch, W, nullptr, out, s_scratch, col_scale, bias, bias_kind, M, N, K, cs);
+  return launch_int8_gemm(q_scratch, W, nullptr, out, s_scratch, col_scale, bias, bias_kind, nullptr, nullptr, M, N, K, cs);
 }

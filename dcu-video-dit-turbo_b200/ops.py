@@ -203,6 +203,31 @@ def int8_gemm_dequant(a: torch.Tensor, row_scale: torch.Tensor, w: torch.Tensor,
     return out
 
 
+def int8_gemm_dequant_residual_(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor,
+                                row_scale: torch.Tensor, w: torch.Tensor, col_scale: torch.Tensor,
+                                bias: torch.Tensor | None) -> torch.Tensor:
+    """x += gate * dequant(a @ w.T) with the block's roundings, in place on x bf16 [M,N]:
+    the GEMM, its dequant epilogue and the gated residual in one kernel.  Returns x."""
+    _require(a.is_cuda and a.dtype == torch.int8 and w.dtype == torch.int8 and a.is_contiguous()
+             and w.is_contiguous() and a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1],
+             "a int8 [M,K] and w int8 [N,K] must be contiguous CUDA tensors")
+    m, k = a.shape
+    n = w.shape[0]
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(x.shape) == (m, n),
+             "x must be a contiguous CUDA bf16 [M,N] tensor")
+    _require(gate.dtype == torch.bfloat16 and gate.numel() == n and gate.is_contiguous(),
+             "gate must be contiguous bf16 [N]")
+    _require(row_scale.dtype == torch.float32 and col_scale.dtype == torch.float32
+             and row_scale.numel() == m and col_scale.numel() == n
+             and row_scale.is_contiguous() and col_scale.is_contiguous(), "scale mismatch")
+    kind = _bias_kind(bias, n, a.device)
+    if m and n:
+        _call("b2_int8_gemm_dequant_residual", a, a.data_ptr(), row_scale.data_ptr(), w.data_ptr(),
+              col_scale.data_ptr(), _ptr(bias) if kind else None, kind, gate.data_ptr(),
+              x.data_ptr(), m, n, k, _stream(a))
+    return x
+
+
 def int8_linear(x: torch.Tensor, w: torch.Tensor, col_scale: torch.Tensor,
                 bias: torch.Tensor | None = None, input_act: str | None = None,
                 scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:

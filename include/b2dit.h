@@ -108,6 +108,16 @@ int b2_int8_gemm_dequant(const int8_t* A, const float* row_scale, const int8_t* 
                          const float* col_scale, const void* bias, int bias_kind, void* out_bf16,
                          int64_t M, int64_t N, int64_t K, void* stream);
 
+/* The same GEMM with the DiT block's gated residual applied in the epilogue:
+ *   y = the dequantised, biased bf16 value above;  x[m,n] = bf16( x[m,n] + bf16(gate[n]*y) ).
+ * x bf16 [M,N] is updated in place, gate bf16 [N]; y never goes through memory.  Bit-identical
+ * to b2_int8_gemm_dequant followed by b2_gate_residual.  (Fusion of two steps of
+ * _int8_linear_nocopy's caller; the reference has no source for the residual itself.) */
+int b2_int8_gemm_dequant_residual(const int8_t* A, const float* row_scale, const int8_t* W,
+                                  const float* col_scale, const void* bias, int bias_kind,
+                                  const void* gate_bf16, void* x_inout_bf16, int64_t M, int64_t N,
+                                  int64_t K, void* stream);
+
 /* Whole INT8 linear: (activation) -> rowwise quantise -> GEMM -> dequant epilogue.
  * Replaces _int8_linear_nocopy, launcher/benchmark_launcher_v14_hires_int8_candidate.py:960-1067
  * (bf16 output, per-output-channel weight scale, no ConvRot).

@@ -227,6 +227,35 @@ def test_int8_gemm_fused_dequant_bit_exact(cuda_pkg, ref, m, n, k):
     cuda_pkg.ops.check_device_status()
 
 
+@pytest.mark.parametrize("m,n,k", [(5, 8, 16), (129, 264, 144), (257, 264, 144), (770, 520, 400),
+                                   (300, 3072, 3072), (1000, 3072, 8192)])
+def test_int8_gemm_residual_epilogue_bit_exact(cuda_pkg, ref, m, n, k):
+    """GEMM + dequant + gated residual in one kernel equals the oracle's epilogue followed
+    by its gated residual, and the two-kernel GPU route, bit for bit; x is updated in place."""
+    g = torch.Generator().manual_seed(7 * m + n + k)
+    a, w = _rand_i8((m, k), g), _rand_i8((n, k), g)
+    rs = torch.rand((m,), generator=g) * 0.002 + 1e-5
+    cs = torch.rand((n,), generator=g) * 0.002 + 1e-5
+    gate = torch.randn((n,), generator=g).to(torch.bfloat16)
+    x = torch.randn((m, n), generator=g).to(torch.bfloat16)
+    acc = ref.int8_mm(a, w)
+    ops = cuda_pkg.ops
+    for bias in (None, torch.randn((n,), generator=g).to(torch.bfloat16), torch.randn((n,), generator=g)):
+        want = ref.gate_residual(x, ref.epilogue(acc, rs, cs, bias), gate)
+        bd = None if bias is None else bias.to(DEV)
+        xd = x.to(DEV)
+        ret = ops.int8_gemm_dequant_residual_(xd, gate.to(DEV), a.to(DEV), rs.to(DEV), w.to(DEV), cs.to(DEV), bd)
+        assert ret.data_ptr() == xd.data_ptr()
+        assert torch.equal(bits(xd.cpu()), bits(want)), (m, n, k)
+        x2 = x.to(DEV)
+        ops.gate_residual_(x2, ops.int8_gemm_dequant(a.to(DEV), rs.to(DEV), w.to(DEV), cs.to(DEV), bd), gate.to(DEV))
+        assert torch.equal(bits(x2.cpu()), bits(want))
+    with pytest.raises(RuntimeError):
+        ops.int8_gemm_dequant_residual_(x.to(DEV)[:, :-8], gate.to(DEV), a.to(DEV), rs.to(DEV), w.to(DEV),
+                                        cs.to(DEV), None)
+    ops.check_device_status()
+
+
 def test_config1_quantize_gemm_epilogue_end_to_end(cuda_pkg, ref):
     """Benchmark config 1: X[4096,3072] ~N(0,1), W[3072,3072] ~N(0,0.02) pre-quantised per
     output channel, bias ~N(0,0.01); q, scale bits, int32 acc and bf16 out all bit-exact,
