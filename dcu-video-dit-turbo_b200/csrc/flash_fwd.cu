@@ -10,24 +10,28 @@
 //
 //   One CTA owns TWO 128-row query tiles of one (batch, head) and walks the KV
 //   sequence in 128-row steps.
-//     warp 0       MMA issuer: S = Q.K^T (tcgen05.mma kind::f16, operands in shared
-//                  memory) and O += P.V (P read from tensor memory, V from shared
-//                  memory as an MN-major operand); accumulators S0,S1,O0,O1 fill the
-//                  512 tensor-memory columns; descriptors are pre-built so that an MMA
-//                  costs the issuing thread three instructions
-//     warp 1       TMA loader: Q once, K and V tiles through a two-stage ring
-//                  (128-byte swizzle; plain per-CTA loads, no multicast)
-//     warps 2-9    softmax for query tile 0, TWO threads per row: warp w and warp w+4
+//     warps 0-7    softmax for query tile 0, TWO threads per row: warp w and warp w+4
 //                  read the same 32 tensor-memory lanes and split the 128 S columns
 //                  64/64, so two instruction streams share each scheduler and the
 //                  exp2 unit stays busy while either one is blocked
-//     warps 10-17  the same for query tile 1
+//     warps 8-15   the same for query tile 1
+//     warp 16      MMA issuer: S = Q.K^T (tcgen05.mma kind::f16, operands in shared
+//                  memory) and O += P.V (P read from tensor memory, V from shared
+//                  memory as an MN-major operand); accumulators S0,S1,O0,O1 fill the
+//                  512 tensor-memory columns
+//     warp 17      TMA loader: Q once, K and V tiles through a two-stage ring
+//                  (128-byte swizzle; plain per-CTA loads, no multicast)
+//     warps 18-19  idle; they complete the service warpgroup, which hands most of its
+//                  registers to the softmax warpgroups (setmaxnreg: 32 vs 112 per thread)
 //   The two tiles ping-pong: while one tile's softmax runs, the tensor core works on
 //   the other tile's MMAs.  P overwrites S in place as bf16.
 //   Per step a thread loads its 64 scores, the two threads of a row exchange their maxima
 //   (shared memory + a 64-thread named barrier) and raise the running max, rescaling O
 //   and l, only when it lags by more than 2^8 in the exp2 domain (rare after the first
-//   steps; the final O/l is exact either way).  P is published in two column halves, each
+//   steps; the final O/l is exact either way).  The scale-and-subtract and the row sum run
+//   as packed f32x2 instructions: the softmax warps are bound by instruction issue, not by
+//   the exp2 unit (moving a share of the exponentials to a polynomial on the FMA pipe was
+//   measured slower at every share).  P is published in two column halves, each
 //   with its own mbarrier, so the tensor core starts O += P.V on the first half while the
 //   second half is still being exponentiated.
 // Every mbarrier wait is bounded; on a timeout the kernel records a status word and
@@ -50,14 +54,23 @@ constexpr int HEAD_DIM = 128;
 constexpr int HALF_BYTES = 128 * 128;        // one [128 rows x 64 bf16] swizzled half tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
 constexpr int KV_STAGES = 2;
-constexpr int kMmaWarp = 0, kLoadWarp = 1, kFirstSoftmaxWarp = 2;
-constexpr int NUM_THREADS = (2 + 16) * 32;   // 576
+constexpr int kFirstSoftmaxWarp = 0, kMmaWarp = 16, kLoadWarp = 17;   // warps 18, 19 idle
+constexpr int NUM_THREADS = (16 + 4) * 32;   // 640: four softmax warpgroups + one service warpgroup
+#ifndef B2_FLASH_REGS_SOFTMAX
+#define B2_FLASH_REGS_SOFTMAX 112
+#endif
+#ifndef B2_FLASH_REGS_SERVICE
+#define B2_FLASH_REGS_SERVICE 32
+#endif
+// setmaxnreg.inc waits, without a limit, until the registers it asks for are free in the
+// CTA's own allocation, so the split must fit into what the kernel was launched with:
+// per scheduler, four softmax warps and one service warp share five launch allocations.
+// The launcher checks this against the compiled register count before every first launch.
+constexpr int kLaunchRegs = 96;   // 65536 / 640 threads, rounded down to the allocation unit of 8
+static_assert(4 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE <= 5 * kLaunchRegs,
+              "register split exceeds the CTA's launch allocation");
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 384;
-#ifndef B2_FLASH_POLY_EVERY
-#define B2_FLASH_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = B2_FLASH_POLY_EVERY;  // every n-th pair takes the polynomial exp2 (0 = none)
 
 constexpr int SMEM_Q = 0;                                   // 2 tiles
 constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;             // KV_STAGES tiles
@@ -89,19 +102,25 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// exp2 on the FMA pipe: round to the nearest integer n with the 1.5*2^23 trick, a
-// degree-3 polynomial for 2^f on f = x - n in [-0.5, 0.5] (max relative error 1.6e-4,
-// below the bf16 rounding that P undergoes anyway), then n added into the exponent field.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.0f);
-  const float t = x + 12582912.0f;
-  const float f = x - (t - 12582912.0f);
-  float p = fmaf(f, 0.05360212177038193f, 0.24237291514873505f);
-  p = fmaf(f, p, 0.6935023665428162f);
-  p = fmaf(f, p, 0.9999481439590454f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+// Packed pairs of fp32 (sm_100 executes one f32x2 instruction for two lanes of work).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
-
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 // rows x 64-element half tiles of one [128 x 128] bf16 tile
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                           int row0, int h, int b, int swap) {
@@ -113,21 +132,6 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
     tma_load_4d(dst, map, bar, 0, row0, h, b);
     tma_load_4d(dst + HALF_BYTES, map, bar, 64, row0, h, b);
   }
-}
-
-// Descriptor LOW-word tables of the MMA issuer, built once per CTA:
-//   Q (A of S = Q.K^T) and K (B): K-major half-tile pairs, 32 bytes of head dim per MMA;
-//   V (B of O += P.V): MN-major, 64-wide d blocks one half tile apart (LBO), 8-row kv
-//   groups 1024 bytes apart (SBO), 16 kv rows = 2048 bytes per MMA.
-__device__ __forceinline__ void build_kmajor_lo(uint32_t (&d)[8], uint32_t tile_addr) {
-  const uint32_t lo = desc_lo(tile_addr, 16);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) d[i] = lo + (i >> 2) * (HALF_BYTES >> 4) + (i & 3) * 2;
-}
-__device__ __forceinline__ void build_v_lo(uint32_t (&d)[8], uint32_t tile_addr) {
-  const uint32_t lo = desc_lo(tile_addr, HALF_BYTES);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) d[i] = lo + i * (2048 >> 4);
 }
 
 constexpr uint32_t kIdescQK = make_idesc(/*f32*/ 1, /*bf16*/ 1, /*bf16*/ 1, 0, 0, BLOCK_M, BLOCK_N);
@@ -170,6 +174,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Registers move from the service warpgroup (MMA issuer, loader, two idle warps) to the
+  // softmax warpgroups: each scheduler holds four softmax warps and one service warp.
+  if (warp >= kMmaWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(B2_FLASH_REGS_SERVICE));
   if (warp == kLoadWarp) {
     // ------------------------------- TMA loader -------------------------------
     if (lane == 0) {
@@ -195,72 +203,69 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (lane == 0) {
       const uint32_t s0 = tmem_base + COL_S0, s1 = tmem_base + COL_S1;
       const uint32_t o0 = tmem_base + COL_O0, o1 = tmem_base + COL_O1;
-      uint32_t q0[8], q1[8], kA[8], kB[8], vA[8], vB[8], pa0[8], pa1[8];
-      build_kmajor_lo(q0, sbase + SMEM_Q);
-      build_kmajor_lo(q1, sbase + SMEM_Q + TILE_BYTES);
-      build_kmajor_lo(kA, sbase + SMEM_K);
-      build_kmajor_lo(kB, sbase + SMEM_K + TILE_BYTES);
-      // P.V tables in PUBLICATION order: the first column half of P covers kv rows
-      // [0,32) and [64,96) (MMAs 0,1,4,5 of the natural order), the second the rest.
-      {
-        uint32_t va[8], vb[8];
-        build_v_lo(va, sbase + SMEM_V);
-        build_v_lo(vb, sbase + SMEM_V + TILE_BYTES);
-        constexpr int order[8] = {0, 1, 4, 5, 2, 3, 6, 7};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          vA[i] = va[order[i]];
-          vB[i] = vb[order[i]];
-          pa0[i] = s0 + order[i] * 8;  // P: 8 tensor-memory columns (16 bf16 of kv) per MMA
-          pa1[i] = s1 + order[i] * 8;
-        }
-      }
+      // Descriptor low words are derived from six base words right where an MMA batch is
+      // issued (a handful of integer adds per batch), so the issuer needs few registers.
+      const uint32_t q0 = desc_lo(sbase + SMEM_Q, 16), q1 = desc_lo(sbase + SMEM_Q + TILE_BYTES, 16);
+      const uint32_t kA = desc_lo(sbase + SMEM_K, 16), kB = desc_lo(sbase + SMEM_K + TILE_BYTES, 16);
+      const uint32_t vA = desc_lo(sbase + SMEM_V, HALF_BYTES);
+      const uint32_t vB = desc_lo(sbase + SMEM_V + TILE_BYTES, HALF_BYTES);
+      // S = Q.K^T: K-major half-tile pairs, 32 bytes of head dim per MMA
+      auto issue_qk = [&](uint32_t d, uint32_t q_lo, uint32_t k_lo) {
+        mma_f16_ss_kmajor_x8(d, q_lo, k_lo, kIdescQK);
+      };
+      // O += P.V for one published column half of P (group 0: kv rows [0,32) and [64,96),
+      // MMAs 0,1,4,5 of the natural order; group 1: the rest).  P: 8 tensor-memory columns
+      // (16 bf16 of kv) per MMA; V: MN-major, 16 kv rows = 2048 bytes per MMA.
+      auto issue_pv = [&](uint32_t d, uint32_t p_base, uint32_t v_lo, const int group, uint32_t acc) {
+        if (group == 0)
+          mma_f16_ts_x4<0>(d, p_base, v_lo, kIdescPV, acc);
+        else
+          mma_f16_ts_x4<2>(d, p_base, v_lo, kIdescPV, acc);
+      };
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, kStatusFlashTimeout) &&
                 mbar_wait(bar(K_FULL), 0, abort_flag, kStatusFlashTimeout);
       if (ok) {
         tc_fence_after();
-        mma_f16_ss_lo_x8(s0, q0, kA, kIdescQK);
+        issue_qk(s0, q0, kA);
         tc_commit(bar(S_FULL));
         ok = mbar_wait(bar(Q_FULL + 1), 0, abort_flag, kStatusFlashTimeout);
       }
       if (ok) {
         tc_fence_after();
-        mma_f16_ss_lo_x8(s1, q1, kA, kIdescQK);
+        issue_qk(s1, q1, kA);
         tc_commit(bar(S_FULL + 1));
         tc_commit(bar(K_EMPTY));
       }
-      // One kv step.  `st` (ring stage of step j) is a literal at both call sites so the
-      // tables are indexed at compile time; the next step's K sits in the other stage.
-      auto step = [&](const int j, const uint32_t (&vd)[8], const uint32_t (&kd_next)[8],
-                      const int st) -> bool {
+      // One kv step; `st` is the ring stage of step j, the next step's K sits in the other.
+      auto step = [&](const int j, const uint32_t vd, const uint32_t kd_next, const int st) -> bool {
         const bool last = j + 1 == n_kv;
         const int st2 = st ^ 1;
         if (!mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
         if (!mbar_wait(bar(P_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        mma_f16_ts_lo_x4(o0, pa0, vd, kIdescPV, j != 0);
+        issue_pv(o0, s0, vd, 0, j != 0);
         if (!mbar_wait(bar(PB_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        mma_f16_ts_lo_x4(o0, pa0 + 4, vd + 4, kIdescPV, 1);
+        issue_pv(o0, s0, vd, 1, 1);
         if (last) {
           tc_commit(bar(O_FULL));
         } else {
           if (!mbar_wait(bar(K_FULL + st2), ((j + 1) >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
           tc_fence_after();
-          mma_f16_ss_lo_x8(s0, q0, kd_next, kIdescQK);
+          issue_qk(s0, q0, kd_next);
           tc_commit(bar(S_FULL));
         }
         if (!mbar_wait(bar(P_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        mma_f16_ts_lo_x4(o1, pa1, vd, kIdescPV, j != 0);
+        issue_pv(o1, s1, vd, 0, j != 0);
         if (!mbar_wait(bar(PB_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
-        mma_f16_ts_lo_x4(o1, pa1 + 4, vd + 4, kIdescPV, 1);
+        issue_pv(o1, s1, vd, 1, 1);
         tc_commit(bar(V_EMPTY + st));
         if (last) {
           tc_commit(bar(O_FULL + 1));
         } else {
-          mma_f16_ss_lo_x8(s1, q1, kd_next, kIdescQK);
+          issue_qk(s1, q1, kd_next);
           tc_commit(bar(S_FULL + 1));
           tc_commit(bar(K_EMPTY + st2));
         }
@@ -271,7 +276,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (ok && j + 1 < n_kv) ok = step(j + 1, vB, kA, 1);
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(B2_FLASH_REGS_SOFTMAX));
     // ---------------- softmax + output: two threads per row, 64 columns each ----------------
     const int ws = warp - kFirstSoftmaxWarp;
     const int t = ws >> 3;              // query tile
@@ -348,22 +355,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       const float neg_ms = -row_max * sl2;
-      float sm[4] = {0.f, 0.f, 0.f, 0.f};
+      // exponentials on packed pairs: one f32x2 FMA and one f32x2 add per two scores
+      const uint64_t sl2x2 = pack2(sl2, sl2), nmsx2 = pack2(neg_ms, neg_ms);
+      uint64_t sm2[4] = {0ull, 0ull, 0ull, 0ull};
       // two column halves of 32 scores, each published as soon as it is written
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t p[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float e0, e1;
-          if (kPolyEvery != 0 && ((c >> 1) % (kPolyEvery ? kPolyEvery : 1)) == 0) {
-            e0 = ex2_poly(fmaf(__uint_as_float(s[32 * hh + c]), sl2, neg_ms));
-            e1 = ex2_poly(fmaf(__uint_as_float(s[32 * hh + c + 1]), sl2, neg_ms));
-          } else {
-            e0 = ex2_approx(fmaf(__uint_as_float(s[32 * hh + c]), sl2, neg_ms));
-            e1 = ex2_approx(fmaf(__uint_as_float(s[32 * hh + c + 1]), sl2, neg_ms));
-          }
-          sm[(c >> 1) & 3] += e0 + e1;
+          const uint64_t xx = fma2(pack2(__uint_as_float(s[32 * hh + c]), __uint_as_float(s[32 * hh + c + 1])),
+                                   sl2x2, nmsx2);
+          float x0, x1;
+          unpack2(xx, x0, x1);
+          const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+          sm2[(c >> 1) & 3] = add2(sm2[(c >> 1) & 3], pack2(e0, e1));
           p[c >> 1] = pack_bf16x2_rn(e0, e1);
         }
         tmem_st_32x32b_x16(p_tmem + 16 * hh, p);
@@ -372,7 +378,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         __syncwarp();
         if (lane == 0) mbar_arrive(bar((hh ? PB_FULL : P_FULL) + t));  // one arrival per warp, 8 per tile
       }
-      row_sum += (sm[0] + sm[1]) + (sm[2] + sm[3]);
+      {
+        float a0, a1, b0, b1, c0, c1, d0, d1;
+        unpack2(sm2[0], a0, a1);
+        unpack2(sm2[1], b0, b1);
+        unpack2(sm2[2], c0, c1);
+        unpack2(sm2[3], d0, d1);
+        row_sum += ((a0 + a1) + (b0 + b1)) + ((c0 + c1) + (d0 + d1));
+      }
     }
     // ---- final: O / l -> bf16 -> global (BSHD); l = both halves' sums ----
     if (ok) ok = mbar_wait(bar(O_FULL + t), 0, abort_flag, kStatusFlashTimeout);
@@ -491,6 +504,12 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_TOTAL);
     if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "flash_fwd: smem attribute: %s", cudaGetErrorString(e));
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, flash_fwd_kernel);
+    if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "flash_fwd: attributes: %s", cudaGetErrorString(e));
+    if (4 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE > 5 * ((fa.numRegs + 7) / 8 * 8))
+      return fail(B2_LAUNCH_FAILED, "flash_fwd: register split %d/%d does not fit %d launch registers",
+                  B2_FLASH_REGS_SOFTMAX, B2_FLASH_REGS_SERVICE, fa.numRegs);
     attr_set = true;
   }
   if (H > 65535 || B > 65535) return fail(B2_TOO_LARGE, "flash_fwd: heads/batch exceed the launch grid");

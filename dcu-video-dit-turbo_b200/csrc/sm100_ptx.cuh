@@ -73,6 +73,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // leave their loops and fall through to the common teardown.  The bound is a poll COUNT,
 // not a clock reading: special-register reads are slow when the SM's transcendental unit
 // is saturated, and these waits sit on the tensor pipe's critical path.
+// (Measured on the attention kernel: a tighter poll loop takes issue slots from the
+// arithmetic warps, -15%; a long try_wait suspend hint wakes the warp late, -5%.)
 constexpr uint32_t kWaitPollLimit = 1u << 26;   // suspending try_wait polls (>= ~1 s)
 constexpr uint32_t kSpinPollLimit = 1u << 27;   // non-suspending test_wait polls (~1-2 s)
 
@@ -373,6 +375,58 @@ __device__ __forceinline__ void mma_f16_ts_lo_x4(uint32_t d_tmem, const uint32_t
       : "memory");
 }
 #undef B2_TS_LO
+
+// Eight / four MMAs whose descriptor low words are `base + compile-time offset`: the adds
+// sit inside the asm block, next to their MMA, so the compiler cannot hoist sixteen
+// loop-invariant words per batch into registers (the issuing warp runs on a small
+// register budget).
+#define B2_SS_BASE(off, pred)                                                      \
+  "add.u32 ra, %1, " #off "; add.u32 rb, %2, " #off ";\n\t"                        \
+  "mov.b64 da, {ra, %3}; mov.b64 db, {rb, %3};\n\t"                               \
+  "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, " pred ";\n\t"
+// K-major 128-row operands in two 64-element half tiles 16384 bytes apart (1024 in
+// descriptor units), 32 bytes (2 units) of K per MMA.
+__device__ __forceinline__ void mma_f16_ss_kmajor_x8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                     uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 da, db;\n\t"
+      ".reg .b32 ra, rb;\n\t"
+      "setp.ne.b32 p0, 0, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t" B2_SS_BASE(0, "p0") B2_SS_BASE(2, "p1") B2_SS_BASE(4, "p1")
+          B2_SS_BASE(6, "p1") B2_SS_BASE(1024, "p1") B2_SS_BASE(1026, "p1") B2_SS_BASE(1028, "p1")
+              B2_SS_BASE(1030, "p1") "}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc)
+      : "memory");
+}
+#undef B2_SS_BASE
+// Four MMAs with A in tensor memory: MMA i reads A at a_tmem + M_i*8 columns and B at
+// b_lo + M_i*128 descriptor units, M = {M0, M0+1, M0+4, M0+5}.
+template <int M0>
+__device__ __forceinline__ void mma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 db;\n\t"
+      ".reg .b32 ra, rb;\n\t"
+      "setp.ne.b32 p0, %5, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "add.u32 ra, %1, %6; add.u32 rb, %2, %7; mov.b64 db, {rb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p0;\n\t"
+      "add.u32 ra, %1, %8; add.u32 rb, %2, %9; mov.b64 db, {rb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+      "add.u32 ra, %1, %10; add.u32 rb, %2, %11; mov.b64 db, {rb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+      "add.u32 ra, %1, %12; add.u32 rb, %2, %13; mov.b64 db, {rb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(accumulate),
+      "n"(M0 * 8), "n"(M0 * 128), "n"((M0 + 1) * 8), "n"((M0 + 1) * 128), "n"((M0 + 4) * 8),
+      "n"((M0 + 4) * 128), "n"((M0 + 5) * 8), "n"((M0 + 5) * 128)
+      : "memory");
+}
 
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
