@@ -200,7 +200,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop and one elected lane issues the MMAs and commits: with
+    // no lane-divergent region around them, addresses and descriptors stay warp-uniform.
+    const bool leader = elect_one() != 0;
+    {
       const uint32_t s0 = tmem_base + COL_S0, s1 = tmem_base + COL_S1;
       const uint32_t o0 = tmem_base + COL_O0, o1 = tmem_base + COL_O1;
       // Descriptor low words are derived from six base words right where an MMA batch is
@@ -211,36 +214,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint32_t vB = desc_lo(sbase + SMEM_V + TILE_BYTES, HALF_BYTES);
       // S = Q.K^T: K-major half-tile pairs, 32 bytes of head dim per MMA
       auto issue_qk = [&](uint32_t d, uint32_t q_lo, uint32_t k_lo) {
-        mma_f16_ss_kmajor_x8(d, q_lo, k_lo, kIdescQK);
+        if (leader) mma_f16_ss_kmajor_x8(d, q_lo, k_lo, kIdescQK);
       };
       // O += P.V for one published column half of P (group 0: kv rows [0,32) and [64,96),
       // MMAs 0,1,4,5 of the natural order; group 1: the rest).  P: 8 tensor-memory columns
       // (16 bf16 of kv) per MMA; V: MN-major, 16 kv rows = 2048 bytes per MMA.
       auto issue_pv = [&](uint32_t d, uint32_t p_base, uint32_t v_lo, const int group, uint32_t acc) {
-        if (group == 0)
-          mma_f16_ts_x4<0>(d, p_base, v_lo, kIdescPV, acc);
-        else
-          mma_f16_ts_x4<2>(d, p_base, v_lo, kIdescPV, acc);
+        if (leader) {
+          if (group == 0)
+            mma_f16_ts_x4<0>(d, p_base, v_lo, kIdescPV, acc);
+          else
+            mma_f16_ts_x4<2>(d, p_base, v_lo, kIdescPV, acc);
+        }
       };
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, kStatusFlashTimeout) &&
                 mbar_wait(bar(K_FULL), 0, abort_flag, kStatusFlashTimeout);
       if (ok) {
         tc_fence_after();
         issue_qk(s0, q0, kA);
-        tc_commit(bar(S_FULL));
+        if (leader) tc_commit(bar(S_FULL));
         ok = mbar_wait(bar(Q_FULL + 1), 0, abort_flag, kStatusFlashTimeout);
       }
       if (ok) {
         tc_fence_after();
         issue_qk(s1, q1, kA);
-        tc_commit(bar(S_FULL + 1));
-        tc_commit(bar(K_EMPTY));
+        if (leader) tc_commit(bar(S_FULL + 1));
+        if (leader) tc_commit(bar(K_EMPTY));
       }
       // One kv step; `st` is the ring stage of step j, the next step's K sits in the other.
       auto step = [&](const int j, const uint32_t vd, const uint32_t kd_next, const int st) -> bool {
         const bool last = j + 1 == n_kv;
         const int st2 = st ^ 1;
-        if (!mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
         if (!mbar_wait(bar(P_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
         issue_pv(o0, s0, vd, 0, j != 0);
@@ -248,12 +252,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
         issue_pv(o0, s0, vd, 1, 1);
         if (last) {
-          tc_commit(bar(O_FULL));
+          if (leader) tc_commit(bar(O_FULL));
         } else {
           if (!mbar_wait(bar(K_FULL + st2), ((j + 1) >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
           tc_fence_after();
           issue_qk(s0, q0, kd_next);
-          tc_commit(bar(S_FULL));
+          if (leader) tc_commit(bar(S_FULL));
         }
         if (!mbar_wait(bar(P_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
@@ -261,16 +265,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!mbar_wait(bar(PB_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
         tc_fence_after();
         issue_pv(o1, s1, vd, 1, 1);
-        tc_commit(bar(V_EMPTY + st));
+        if (leader) tc_commit(bar(V_EMPTY + st));
         if (last) {
-          tc_commit(bar(O_FULL + 1));
+          if (leader) tc_commit(bar(O_FULL + 1));
         } else {
+          // next step's V: waited for here, while the tensor core still has this step's MMAs
+          // queued, so the wait is off the path between this step's last and the next step's
+          // first MMA
+          if (!mbar_wait(bar(V_FULL + st2), ((j + 1) >> 1) & 1, abort_flag, kStatusFlashTimeout)) return false;
           issue_qk(s1, q1, kd_next);
-          tc_commit(bar(S_FULL + 1));
-          tc_commit(bar(K_EMPTY + st2));
+          if (leader) tc_commit(bar(S_FULL + 1));
+          if (leader) tc_commit(bar(K_EMPTY + st2));
         }
         return true;
       };
+      if (ok) ok = mbar_wait(bar(V_FULL), 0, abort_flag, kStatusFlashTimeout);
       for (int j = 0; ok && j < n_kv; j += 2) {
         ok = step(j, vA, kB, 0);
         if (ok && j + 1 < n_kv) ok = step(j + 1, vB, kA, 1);
