@@ -40,6 +40,8 @@ SYMBOLS = {
     "b2_layernorm_mod": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp]),
     "b2_layernorm_mod_quant": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp]),
     "b2_qk_norm_rope": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp]),
+    "b2_qk_norm_rope_pack": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
+    "b2_quantize_int8_rowwise_gathered": (_int, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "b2_gate_residual": (_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
 }
 

@@ -101,9 +101,16 @@ class DiTBlock:
         q8, s = ops.layernorm_mod_quant(x, p["scale1"], p["shift1"])
         qkv = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_qkv"], p["ws_qkv"], p["b_qkv"])
         qkv = qkv.view(L, 3, self.heads, self.head_dim)
-        ops.qk_norm_rope_(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin)
-        o = self.attention(qkv)
-        q8, s = ops.quantize_int8_rowwise(o)
+        if self.sp is not None and self.sp.world > 1:
+            # sequence parallel: norm + rotary write the all-to-all send buffer directly and
+            # the out-projection's quantizer reads the reverse all-to-all's buffer in place
+            send = ops.qk_norm_rope_pack(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin,
+                                         self.sp.world, self.head_chunks)
+            q8, s = ops.quantize_int8_rowwise_gathered(
+                self.sp.attention_packed(send, self._attn, overlap=self.overlap))
+        else:
+            ops.qk_norm_rope_(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin)
+            q8, s = ops.quantize_int8_rowwise(self.attention(qkv))
         ops.int8_gemm_dequant_residual_(x, p["gate1"], q8, s.view(-1), p["wq_out"], p["ws_out"], p["b_out"])
         q8, s = ops.layernorm_mod_quant(x, p["scale2"], p["shift2"])
         f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])

@@ -185,6 +185,33 @@ int b2_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* cos_
   return launch_qk_norm_rope(qkv, qw, kw, cos_tab, sin_tab, S, H, eps, (cudaStream_t)stream);
 }
 
+int b2_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const void* kw,
+                         const float* cos_tab, const float* sin_tab, int64_t L, int32_t H,
+                         int32_t world, int32_t chunks, float eps, void* stream) {
+  if (L < 0 || H <= 0 || world <= 0 || chunks <= 0 || H % (world * chunks) != 0)
+    return fail(B2_BAD_SHAPE, "qk_norm_rope_pack: world*chunks must divide the head count (L=%lld H=%d world=%d chunks=%d)",
+                (long long)L, H, world, chunks);
+  if (L == 0) return B2_OK;
+  if (!qkv || !send || !qw || !kw || !cos_tab || !sin_tab) return fail(B2_NULL_POINTER, "qk_norm_rope_pack: null pointer");
+  if (!aligned16(qkv) || !aligned16(send) || !aligned16(qw) || !aligned16(kw) || !aligned16(cos_tab) || !aligned16(sin_tab))
+    return fail(B2_BAD_STRIDE, "qk_norm_rope_pack: pointers must be 16-byte aligned");
+  if (qkv == send) return fail(B2_BAD_STRIDE, "qk_norm_rope_pack: the send buffer must not alias the input");
+  if (!(eps >= 0.f)) return fail(B2_BAD_SHAPE, "qk_norm_rope_pack: eps must be non-negative");
+  return launch_qk_norm_rope_pack(qkv, send, qw, kw, cos_tab, sin_tab, L, H, world, chunks, eps, (cudaStream_t)stream);
+}
+
+int b2_quantize_int8_rowwise_gathered(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
+                                      int32_t world, int32_t chunks, void* stream) {
+  if (M < 0 || K <= 0 || world <= 0 || chunks <= 0 || K % ((int64_t)world * chunks * 8) != 0 || K > 16384)
+    return fail(B2_BAD_SHAPE, "quantize_int8_rowwise_gathered: K=%lld must be a multiple of 8*world*chunks (world=%d chunks=%d), at most 16384",
+                (long long)K, world, chunks);
+  if (M == 0) return B2_OK;
+  if (!x || !q || !scale) return fail(B2_NULL_POINTER, "quantize_int8_rowwise_gathered: null pointer");
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7u))
+    return fail(B2_BAD_STRIDE, "quantize_int8_rowwise_gathered: x must be 16-byte and q 8-byte aligned");
+  return launch_quantize_gathered(x, q, scale, M, K, world, chunks, (cudaStream_t)stream);
+}
+
 static int check_gemm(const char* who, const int8_t* A, const int8_t* W, int64_t M, int64_t N,
                       int64_t K, int n_mult) {
   if (M < 0 || N < 0 || K < 0) return fail(B2_BAD_SHAPE, "%s: negative size", who);

@@ -8,6 +8,9 @@ namespace b2 {
 
 int launch_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                     cudaStream_t stream);
+// world > 0: source rows gathered from [chunks][world][M][K / (world*chunks)]
+int launch_quantize_gathered(const void* x, int8_t* q, float* scale, int64_t M, int64_t K, int world,
+                             int chunks, cudaStream_t stream);
 int launch_swiglu_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                            cudaStream_t stream);
 int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t stream);
@@ -22,6 +25,9 @@ int launch_layernorm_mod(const void* x, const void* scale, const void* shift, vo
                          bool quant, cudaStream_t stream);
 int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* cos_tab,
                         const float* sin_tab, int64_t S, int H, float eps, cudaStream_t stream);
+int launch_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const void* kw,
+                             const float* cos_tab, const float* sin_tab, int64_t L, int H, int world,
+                             int chunks, float eps, cudaStream_t stream);
 // out_i32 != nullptr: plain int32 result.  Otherwise the fused dequant epilogue writes
 // bf16 to out_bf16, or, with gate/residual non-null, x = bf16(x + bf16(gate*y)) in place.
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,

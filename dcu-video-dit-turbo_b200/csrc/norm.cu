@@ -198,6 +198,57 @@ qk_norm_rope_kernel(uint4* __restrict__ qkv, const uint4* __restrict__ qw,
   }
 }
 
+// The same normalisation and rotation, written straight into the send buffer of the
+// sequence-parallel all-to-all instead of in place: qkv bf16 [L,3,H,128] -> send
+// [chunks][world][L][c][3][128] with head h = (p*chunks + ch)*c + ci (rank p receives its
+// heads of every chunk), V copied unchanged.  16 threads per (row, part in {q,k,v}, head).
+__global__ void __launch_bounds__(kThreads)
+qk_norm_rope_pack_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ send,
+                         const uint4* __restrict__ qw, const uint4* __restrict__ kw,
+                         const float4* __restrict__ cos_tab, const float4* __restrict__ sin_tab,
+                         int64_t L, int H, int world, int chunks, float eps) {
+  const int64_t total = L * 3 * H * 16;
+  const int c_heads = H / (world * chunks);
+  for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; (t & ~(int64_t)31) < total;
+       t += (int64_t)gridDim.x * kThreads) {
+    const bool live = t < total;
+    const int64_t tt = live ? t : total - 1;
+    const int l = (int)(tt & 15);
+    const int64_t hv = tt >> 4;
+    const int h = (int)(hv % H);
+    const int part = (int)((hv / H) % 3);
+    const int64_t s = hv / (3 * H);
+    const uint4 v = ldg_stream(qkv + ((s * 3 + part) * H + h) * 16 + l);
+    const int seg = h / c_heads, ci = h - seg * c_heads;     // seg = p*chunks + ch
+    const int p = seg / chunks, ch = seg - p * chunks;
+    uint4* dst = send + (((((int64_t)ch * world + p) * L + s) * c_heads + ci) * 3 + part) * 16 + l;
+    // every lane takes part in the shuffles; V lanes discard the result
+    const uint4 wv = (part == 1 ? kw : qw)[l];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    float e[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      e[2 * j] = bf16lo_to_f32(w[j]);
+      e[2 * j + 1] = bf16hi_to_f32(w[j]);
+      ss += e[2 * j] * e[2 * j] + e[2 * j + 1] * e[2 * j + 1];
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float rms = rsqrtf(ss * (1.0f / 128.0f) + eps);
+    const float4 c = cos_tab[s * 16 + l], sn = sin_tab[s * 16 + l];
+    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y0 = e[2 * j] * rms * bf16lo_to_f32(ww[j]);
+      const float y1 = e[2 * j + 1] * rms * bf16hi_to_f32(ww[j]);
+      o[j] = pack_bf16x2_rn(y0 * cc[j] - y1 * sv[j], y1 * cc[j] + y0 * sv[j]);
+    }
+    if (live) *dst = part == 2 ? v : make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 int grid_for_rows(int64_t M, int rows_per_cta, int ctas_per_sm) {
   int64_t need = (M + rows_per_cta - 1) / rows_per_cta;
   int64_t cap = (int64_t)kNumSMsB200 * ctas_per_sm;
@@ -245,6 +296,19 @@ int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* 
       (uint4*)qkv, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab,
       (const float4*)sin_tab, S, H, eps);
   return check_launch("qk_norm_rope");
+}
+
+int launch_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const void* kw,
+                             const float* cos_tab, const float* sin_tab, int64_t L, int H, int world,
+                             int chunks, float eps, cudaStream_t stream) {
+  const int64_t total = L * 3 * H * 16;
+  int64_t blocks = (total + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)kNumSMsB200 * 32;
+  if (blocks > cap) blocks = cap;
+  qk_norm_rope_pack_kernel<<<(int)blocks, kThreads, 0, stream>>>(
+      (const uint4*)qkv, (uint4*)send, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab,
+      (const float4*)sin_tab, L, H, world, chunks, eps);
+  return check_launch("qk_norm_rope_pack");
 }
 
 }  // namespace b2

@@ -36,13 +36,30 @@ __device__ __forceinline__ float row_allreduce_max(float v, float* smem) {
   return v;
 }
 
+// Where a row's vectors come from.  Contiguous: x[row, :].  Gathered: the row is spread
+// over world*chunks segments of seg_vec vectors in a buffer laid out
+// [chunks][world][M][seg_vec] (what the reverse all-to-all of sequence-parallel attention
+// delivers: segment (p, ch) holds heads p*H/world + ch*c .. +c of the row), so the
+// quantizer reads the exchange buffer in place and no unpack copy is made.
+struct RowGather {
+  int seg_vec;   // 0: contiguous
+  int chunks;
+  int world;
+};
+__device__ __forceinline__ int64_t source_vec(const RowGather& g, int64_t row, int64_t M, int kvec, int c) {
+  if (g.seg_vec == 0) return row * kvec + c;
+  const int seg = c / g.seg_vec, w = c - seg * g.seg_vec;
+  const int p = seg / g.chunks, ch = seg - p * g.chunks;
+  return (((int64_t)ch * g.world + p) * M + row) * g.seg_vec + w;
+}
+
 // One row per TPR threads, VPT 16-byte vectors (8 bf16) per thread, K % 8 == 0,
 // K <= TPR*VPT*8.  Rows are assigned round-robin to row slots over a grid-stride
 // loop so a fixed, SM-count-sized grid covers any M.
 template <int TPR, int VPT>
 __global__ void __launch_bounds__(kThreads)
 quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __restrict__ scales,
-                     int64_t M, int kvec) {
+                     int64_t M, int kvec, const RowGather gather) {
   __shared__ float red[kThreads / 32];
   constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
   const int slot = threadIdx.x / TPR;
@@ -51,11 +68,11 @@ quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* 
     const int64_t row = row0 + slot;
     const bool live = row < M;
     uint4 v[VPT];
-    const uint4* xr = x + row * kvec;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + i * TPR;
-      v[i] = (live && c < kvec) ? ldg_stream(xr + c) : make_uint4(0, 0, 0, 0);
+      v[i] = (live && c < kvec) ? ldg_stream(x + source_vec(gather, row, M, kvec, c))
+                                : make_uint4(0, 0, 0, 0);
     }
     uint32_t acc = 0;
 #pragma unroll
@@ -250,14 +267,21 @@ int grid_for_rows(int64_t M, int rows_per_cta, int ctas_per_sm) {
 
 }  // namespace
 
-// Picks the register-resident variant for K, or the generic kernel.
-int launch_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
-                    cudaStream_t stream) {
+// Picks the register-resident variant for K, or the generic kernel.  world > 0 selects the
+// gathered source layout [chunks][world][M][K / (world*chunks)] (vector path only; the
+// caller has checked the shape).
+int launch_quantize_gathered(const void* x, int8_t* q, float* scale, int64_t M, int64_t K, int world,
+                             int chunks, cudaStream_t stream) {
   const bool vec_ok = (K % 8 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
   const int kvec = (int)(K / 8);
+  RowGather gather{0, 1, 1};
+  if (world > 0) {
+    if (!vec_ok || K > 16384) return fail(B2_BAD_SHAPE, "quantize_int8_rowwise_gathered: K must be a multiple of 8, at most 16384");
+    gather = RowGather{kvec / (world * chunks), chunks, world};
+  }
 #define B2_Q(TPR, VPT)                                                                     \
   quantize_rows_kernel<TPR, VPT><<<grid_for_rows(M, kThreads / TPR, 8), kThreads, 0, stream>>>( \
-      (const uint4*)x, (uint2*)q, scale, M, kvec)
+      (const uint4*)x, (uint2*)q, scale, M, kvec, gather)
   if (vec_ok && K <= 1024) B2_Q(32, 4);
   else if (vec_ok && K <= 2048) B2_Q(32, 8);
   else if (vec_ok && K <= 3072) B2_Q(32, 12);
@@ -270,6 +294,11 @@ int launch_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K
         (const __nv_bfloat16*)x, q, scale, M, K);
 #undef B2_Q
   return check_launch("quantize_int8_rowwise");
+}
+
+int launch_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
+                    cudaStream_t stream) {
+  return launch_quantize_gathered(x, q, scale, M, K, 0, 1, stream);
 }
 
 int launch_swiglu_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,

@@ -343,6 +343,53 @@ def qk_norm_rope_(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Ten
     return qkv
 
 
+def qk_norm_rope_pack(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor,
+                      cos: torch.Tensor, sin: torch.Tensor, world: int, chunks: int = 1,
+                      eps: float = 1e-6) -> torch.Tensor:
+    """qk_norm_rope_ fused with the pack of the sequence-parallel all-to-all: reads packed
+    qkv bf16 [L,3,H,128] (left untouched) and returns the send buffer
+    [chunks, world, L, c, 3, 128], c = H/(world*chunks); slice [ch] is one all-to-all."""
+    _require(qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 4
+             and qkv.is_contiguous() and qkv.shape[1] == 3 and qkv.shape[3] == 128,
+             "qkv must be a contiguous CUDA bf16 [L,3,H,128] tensor")
+    L, _, h, _ = qkv.shape
+    _require(world > 0 and chunks > 0 and h % (world * chunks) == 0,
+             "world*chunks must divide the head count")
+    _require(cos.dtype == torch.float32 and sin.dtype == torch.float32
+             and tuple(cos.shape) == (L, 64) and tuple(sin.shape) == (L, 64)
+             and cos.is_contiguous() and sin.is_contiguous(), "cos/sin must be fp32 [L,64]")
+    _require(q_weight.numel() == 128 and k_weight.numel() == 128
+             and q_weight.dtype == torch.bfloat16 and k_weight.dtype == torch.bfloat16,
+             "norm weights must be bf16 [128]")
+    c = h // (world * chunks)
+    send = torch.empty((chunks, world, L, c, 3, 128), dtype=torch.bfloat16, device=qkv.device)
+    if L:
+        _call("b2_qk_norm_rope_pack", qkv, qkv.data_ptr(), send.data_ptr(), q_weight.data_ptr(),
+              k_weight.data_ptr(), cos.data_ptr(), sin.data_ptr(), L, h, world, chunks, eps,
+              _stream(qkv))
+    return send
+
+
+def quantize_int8_rowwise_gathered(x: torch.Tensor):
+    """The rowwise quantizer reading the reverse all-to-all's receive buffer in place:
+    x bf16 [chunks, world, M, w] (or [chunks, world, M, c, D]) holds row m's columns ((p*chunks + ch)*w ...) in segment
+    (ch, p).  Returns [int8 [M, K], fp32 [M,1]] with K = chunks*world*w, identical to
+    quantize_int8_rowwise of the unpacked [M,K] tensor."""
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() in (4, 5) and x.is_contiguous(),
+             "input must be a contiguous CUDA bf16 [chunks, world, M, w] (or [..., c, D]) tensor")
+    if x.dim() == 5:
+        x = x.view(x.shape[0], x.shape[1], x.shape[2], x.shape[3] * x.shape[4])
+    chunks, world, m, w = x.shape
+    k = chunks * world * w
+    _require(w % 8 == 0 and 0 < k <= 16384, "segment width must be a multiple of 8 and K <= 16384")
+    q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+    s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
+    if m:
+        _call("b2_quantize_int8_rowwise_gathered", x, x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k,
+              world, chunks, _stream(x))
+    return [q, s]
+
+
 def gate_residual_(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     """In place x = bf16(x + bf16(gate*y)); returns x."""
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()

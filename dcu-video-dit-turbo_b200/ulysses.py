@@ -90,6 +90,85 @@ class UlyssesSP:
         q, k, v = recv.unbind(dim=2)
         return tuple(t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
 
+    # -- pre-packed exchange (no pack / unpack copies) ------------------------------------
+    def exchange_packed(self, send: torch.Tensor, async_op: bool = False):
+        """One chunk's all-to-all: send [world, L_r, c, 3, D] (already destination-major)
+        -> receive [S, c, 3, D].  Returns (receive, work)."""
+        _, L, c, three, d = send.shape
+        recv = torch.empty((self.sequence, c, three, d), device=send.device, dtype=send.dtype)
+        work = dist.all_to_all_single(recv.reshape(-1), send.reshape(-1),
+                                      output_split_sizes=[s * c * three * d for s in self.splits],
+                                      input_split_sizes=[L * c * three * d] * self.world,
+                                      group=self.group, async_op=async_op)
+        return recv, work
+
+    def reverse_into(self, out_chunk: torch.Tensor, recv_slot: torch.Tensor, async_op: bool = False):
+        """Reverse all-to-all of one chunk's attention output [S, c, D] (contiguous; rows are
+        already grouped by owner rank) into recv_slot [world, L_r, c, D]."""
+        c, d = out_chunk.shape[1], out_chunk.shape[2]
+        L = self.local_length
+        return dist.all_to_all_single(recv_slot.reshape(-1), out_chunk.reshape(-1),
+                                      output_split_sizes=[L * c * d] * self.world,
+                                      input_split_sizes=[s * c * d for s in self.splits],
+                                      group=self.group, async_op=async_op)
+
+    def attention_packed(self, send: torch.Tensor, attn: Callable, overlap: bool = False) -> torch.Tensor:
+        """Sequence-parallel attention on a pre-packed send buffer [chunks, world, L_r, c, 3, D]
+        (what ops.qk_norm_rope_pack writes).  Per chunk: all-to-all, attention over the c
+        local heads, reverse all-to-all into slot [ch] of the result
+        [chunks, world, L_r, c, D], which ops.quantize_int8_rowwise_gathered (or
+        `unpack_gathered`) reads in place.  With `overlap` the transfers run on a side stream:
+        chunk i's attention overlaps chunk i+1's forward and chunk i-1's reverse transfer."""
+        chunks, world, L, c, _, d = send.shape
+        if world != self.world or L != self.local_length or chunks * c != self.local_heads:
+            raise RuntimeError("send buffer does not match this sequence-parallel group")
+        result = torch.empty((chunks, world, L, c, d), device=send.device, dtype=send.dtype)
+        if overlap and send.is_cuda:
+            main = torch.cuda.current_stream(send.device)
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=send.device)
+            comm = self._comm_stream
+            ready = torch.cuda.Event()
+            ready.record(main)
+            received = []
+            with torch.cuda.stream(comm):
+                comm.wait_event(ready)
+                for ch in range(chunks):
+                    recv, work = self.exchange_packed(send[ch], async_op=True)
+                    work.wait()
+                    done = torch.cuda.Event()
+                    done.record(comm)
+                    received.append((recv, done))
+            for ch, (recv, done) in enumerate(received):
+                main.wait_event(done)
+                recv.record_stream(main)
+                out = attn(*self.chunk_views(recv))           # [1,c,S,D] view of [1,S,c,D]
+                out_ready = torch.cuda.Event()
+                out_ready.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(out_ready)
+                    out.record_stream(comm)
+                    self.reverse_into(out.transpose(1, 2).reshape(self.sequence, c, d), result[ch],
+                                      async_op=True).wait()
+            back = torch.cuda.Event()
+            back.record(comm)
+            main.wait_event(back)
+            send.record_stream(comm)
+            result.record_stream(comm)
+        else:
+            for ch in range(chunks):
+                recv, _ = self.exchange_packed(send[ch])
+                out = attn(*self.chunk_views(recv))
+                self.reverse_into(out.transpose(1, 2).reshape(self.sequence, c, d), result[ch])
+        return result
+
+    @staticmethod
+    def unpack_gathered(result: torch.Tensor) -> torch.Tensor:
+        """[chunks, world, L, c, D] -> [L, H*D] with head h = (p*chunks + ch)*c + ci (a copy;
+        the quantizer reads the gathered layout directly instead)."""
+        chunks, world, L, c, d = result.shape
+        return result.permute(2, 1, 0, 3, 4).reshape(L, world * chunks * c * d)
+
     # -- attention variants -------------------------------------------------------------
     def attention_baseline(self, qkv: torch.Tensor, attn: Callable) -> torch.Tensor:
         """Three all-to-alls, one attention over the local heads, reverse all-to-all.

@@ -172,6 +172,26 @@ int b2_qk_norm_rope(void* qkv_bf16, const void* q_weight_bf16, const void* k_wei
                     const float* cos_tab, const float* sin_tab, int64_t S, int32_t H, float eps,
                     void* stream);
 
+/* The two ends of the sequence-parallel (Ulysses) exchange without their pack / unpack
+ * copies (the reference measures both as ceilings: communication/bench_fused_qkv_alltoall.py,
+ * communication/bench_reverse_unpack_ceiling.py; its packed layout is
+ * benchmarks/bench_sp_head_chunk_overlap.py:140-164).
+ *
+ * b2_qk_norm_rope_pack: b2_qk_norm_rope, but reading qkv bf16 [L,3,H,128] and writing the
+ * all-to-all send buffer bf16 [chunks][world][L][c][3][128], c = H/(world*chunks), head
+ * h = (p*chunks + ch)*c + ci; V is copied unchanged.  Slice [ch] is one all-to-all.
+ *
+ * b2_quantize_int8_rowwise_gathered: b2_quantize_int8_rowwise whose input row m is spread
+ * over the reverse all-to-all's receive buffer bf16 [chunks][world][M][K/(world*chunks)]
+ * (segment (p, ch) holds columns ((p*chunks + ch) * K/(world*chunks)) onward); q int8 [M,K]
+ * and scale fp32 [M] come out exactly as if the row had been contiguous. */
+int b2_qk_norm_rope_pack(const void* qkv_bf16, void* send_bf16, const void* q_weight_bf16,
+                         const void* k_weight_bf16, const float* cos_tab, const float* sin_tab,
+                         int64_t L, int32_t H, int32_t world, int32_t chunks, float eps,
+                         void* stream);
+int b2_quantize_int8_rowwise_gathered(const void* x_bf16, int8_t* q, float* scale, int64_t M,
+                                      int64_t K, int32_t world, int32_t chunks, void* stream);
+
 /* x = bf16(x + bf16(gate[c]*y)) in place on x; x,y bf16 [M,C], gate bf16 [C]. */
 int b2_gate_residual(void* x_bf16, const void* y_bf16, const void* gate_bf16, int64_t M, int64_t C,
                      void* stream);

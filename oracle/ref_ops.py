@@ -246,6 +246,23 @@ def heads_to_sequence_all(heads: list[torch.Tensor], splits: list[int]) -> list[
     return [t.contiguous() for t in full.split(splits, dim=0)]
 
 
+def pack_send(qkv: torch.Tensor, world: int, chunks: int) -> torch.Tensor:
+    """Packed projection output [L,3,H,D] -> destination-major send buffer
+    [chunks, world, L, c, 3, D], c = H/(world*chunks), head h = (p*chunks + ch)*c + ci.
+    Slice [ch] is the [world, L, c, 3, D] buffer of
+    benchmarks/bench_sp_head_chunk_overlap.py:140-164."""
+    L, _, h, d = qkv.shape
+    c = h // (world * chunks)
+    return qkv.reshape(L, 3, world, chunks, c, d).permute(3, 2, 0, 4, 1, 5).contiguous()
+
+
+def unpack_gathered(recv: torch.Tensor) -> torch.Tensor:
+    """Reverse all-to-all receive buffer [chunks, world, L, c, D] -> [L, H*D] in head order
+    h = (p*chunks + ch)*c + ci."""
+    chunks, world, L, c, d = recv.shape
+    return recv.permute(2, 1, 0, 3, 4).reshape(L, world * chunks * c * d).contiguous()
+
+
 # ----------------------------------------------------------------------------
 # DiT block glue.  No reference source exists for these (they live in ComfyUI's
 # model file, which is not part of the reference tree): PARITY UNPINNED.  The

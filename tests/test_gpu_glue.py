@@ -48,6 +48,49 @@ def test_qk_norm_rope(cuda_pkg, ref, s, h):
         assert float((bits(a) != bits(b)).float().mean()) < 0.02
 
 
+@pytest.mark.parametrize("s,h,world,chunks", [(37, 24, 1, 1), (37, 24, 2, 1), (50, 24, 4, 2), (19, 24, 8, 3),
+                                              (33, 24, 2, 3), (5, 4, 2, 2)])
+def test_qk_norm_rope_pack_equals_in_place_then_pack(cuda_pkg, ref, s, h, world, chunks):
+    """The fused norm + rotary + all-to-all pack writes exactly the bits of the in-place
+    kernel followed by the oracle's pack, and leaves its input untouched."""
+    g = torch.Generator().manual_seed(s + h + world + chunks)
+    qkv = torch.randn((s, 3, h, 128), generator=g).to(torch.bfloat16)
+    qw = (1 + torch.randn((128,), generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    kw = (1 + torch.randn((128,), generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    pos = torch.stack((torch.arange(s) // 7, torch.arange(s) % 7, torch.arange(s) % 5), -1)
+    cos, sin = (t.to(DEV) for t in ref.rope_tables(pos))
+    src = qkv.to(DEV)
+    send = cuda_pkg.ops.qk_norm_rope_pack(src, qw, kw, cos, sin, world, chunks)
+    assert tuple(send.shape) == (chunks, world, s, h // (world * chunks), 3, 128)
+    assert torch.equal(bits(src.cpu()), bits(qkv))
+    in_place = qkv.to(DEV)
+    cuda_pkg.ops.qk_norm_rope_(in_place, qw, kw, cos, sin)
+    assert torch.equal(bits(send.cpu()), bits(ref.pack_send(in_place.cpu(), world, chunks)))
+    with pytest.raises(RuntimeError):
+        cuda_pkg.ops.qk_norm_rope_pack(src, qw, kw, cos, sin, 5, 1)
+
+
+@pytest.mark.parametrize("m,k,world,chunks", [(37, 3072, 2, 1), (50, 3072, 4, 2), (19, 3072, 8, 3), (7, 1024, 1, 1),
+                                              (9, 8192, 4, 4), (5, 16384, 2, 1), (3, 64, 2, 2)])
+def test_gathered_quantizer_equals_quantizer_of_unpacked_rows(cuda_pkg, ref, m, k, world, chunks):
+    """Reading the reverse all-to-all's buffer in place gives the bits of quantising the
+    unpacked [M,K] tensor (oracle) - q and scale."""
+    g = torch.Generator().manual_seed(m + k + world)
+    w = k // (world * chunks)
+    recv = (torch.randn((chunks, world, m, w), generator=g) * 3).to(torch.bfloat16)
+    recv[0, 0, 0, :] = 0                      # part of a row that is zero
+    if m > 2:
+        recv[:, :, 2, :] = 0                  # an all-zero row
+    q, s = cuda_pkg.ops.quantize_int8_rowwise_gathered(recv.to(DEV))
+    rows = ref.unpack_gathered(recv.view(chunks, world, m, 1, w))
+    qr, sr = ref.quantize_int8_rowwise(rows)
+    assert torch.equal(q.cpu(), qr) and torch.equal(bits(s.cpu()), bits(sr))
+    q2, s2 = cuda_pkg.ops.quantize_int8_rowwise(rows.to(DEV))
+    assert torch.equal(q2, q) and torch.equal(bits(s2.cpu()), bits(s.cpu()))
+    with pytest.raises(RuntimeError):
+        cuda_pkg.ops.quantize_int8_rowwise_gathered(recv.to(DEV)[..., :-4])
+
+
 @pytest.mark.parametrize("m,c", [(3, 8), (65, 3072), (5, 7)])
 def test_gate_residual_bit_exact(cuda_pkg, ref, m, c):
     g = torch.Generator().manual_seed(m * c)

@@ -56,6 +56,11 @@ def _worker(rank, world, port, seq, result_dir):
                    "fused_serial": sp.attention_fused(mine, attn, chunks=min(hl, 3), overlap=False),
                    "fused_overlap": sp.attention_fused(mine, attn, chunks=min(hl, 3), overlap=True),
                    "fused_overlap_max": sp.attention_fused(mine, attn, chunks=hl, overlap=True)}
+        # pre-packed exchange: destination-major send buffer in, reverse all-to-all layout out
+        for name, chunks, overlap in (("packed1", 1, False), ("packed_overlap", min(hl, 3), True),
+                                      ("packed_overlap_max", hl, True)):
+            packed = sp.attention_packed(ref.pack_send(mine.cpu(), world, chunks).to(dev), attn, overlap=overlap)
+            results[name] = sp.unpack_gathered(packed).view(splits[rank], H, D)
         torch.cuda.synchronize()
         ok = all(torch.equal(t, single) for t in results.values())
         flag = torch.tensor([int(ok)], device=dev, dtype=torch.int32)

@@ -71,6 +71,19 @@ def _worker(rank, world, port, seq, heads, flag_mismatch, result_dir):
         assert torch.equal(base, want)
         for chunks in (1, hl):
             assert torch.equal(sp.attention_fused(mine, attn, chunks=chunks, overlap=False), want)
+        # pre-packed exchange: the send buffer is built destination-major up front (what the
+        # fused norm+rotary+pack kernel writes) and the result stays in the reverse
+        # all-to-all's layout (what the gathered quantizer reads)
+        for chunks in (1, hl):
+            send = ref.pack_send(mine, world, chunks)
+            for ch in range(chunks):
+                recv, _ = sp.exchange_packed(send[ch])
+                legacy, _, _ = sp.pack_chunk(mine, ch * (hl // chunks), (ch + 1) * (hl // chunks), async_op=False)
+                assert torch.equal(recv, legacy)
+            result = sp.attention_packed(send, attn, overlap=False)
+            assert tuple(result.shape) == (chunks, world, splits[rank], hl // chunks, D)
+            assert torch.equal(ref.unpack_gathered(result), want.reshape(splits[rank], heads * D))
+            assert torch.equal(sp.unpack_gathered(result), want.reshape(splits[rank], heads * D))
         Path(result_dir, f"r{rank}.txt").write_text("ok")
     finally:
         dist.destroy_process_group()
