@@ -324,3 +324,32 @@ def test_gated_linear_routes_agree(cuda_pkg, ref):
         pkg.linear.int8_linear(xd[..., :128], wd, wsd, bd, gates=fused)
     with pytest.raises(ValueError, match="scalar or per-output-channel"):
         pkg.linear.int8_linear(xd, wd, wsd[:5], bd, gates=fused)
+
+
+def test_linear_dispatch_routes_quantized_weights_to_the_int8_path(cuda_pkg, ref):
+    """torch.nn.functional.linear on an Int8Weight with a whitelisted shape reaches the INT8
+    kernels (same bits as ops.int8_linear and the oracle); other shapes and a disabled
+    dispatch go to the original handler and are counted."""
+    pkg = cuda_pkg
+    g = torch.Generator().manual_seed(77)
+    w = (torch.randn((3072, 3072), generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn((4096, 3072), generator=g).to(torch.bfloat16)
+    bias = (torch.randn((3072,), generator=g) * 0.01).to(torch.bfloat16)
+    gates = pkg.gates.Gates.all_on()
+    d = pkg.dispatch.LinearDispatch(gates=gates)
+    qw = pkg.dispatch.quantize_weight(w.to(DEV), dispatch=d)
+    wq_ref, ws_ref = ref.quantize_weight_per_channel(w)
+    assert torch.equal(qw.qdata.cpu(), wq_ref) and torch.equal(bits(qw.scale.cpu()), bits(ws_ref))
+    y = torch.nn.functional.linear(x.to(DEV), qw, bias.to(DEV))
+    assert d.summary()["routed"] == 1 and d.summary()["fallbacks"] == {}
+    assert torch.equal(bits(y.cpu()), bits(ref.int8_linear(x, wq_ref, ws_ref, bias)))
+    assert torch.equal(y, pkg.ops.int8_linear(x.to(DEV), qw.qdata, qw.scale, bias.to(DEV)))
+    d.set_enabled(False)
+    y_off = torch.nn.functional.linear(x.to(DEV), qw, bias.to(DEV))
+    assert d.summary()["fallbacks"] == {"disabled": 1}
+    assert torch.equal(y_off, torch.nn.functional.linear(x.to(DEV), qw.dequantize(), bias.to(DEV)))
+    d.set_enabled(True)
+    odd = pkg.dispatch.quantize_weight((torch.randn((40, 64), generator=g)).to(torch.bfloat16).to(DEV), dispatch=d)
+    torch.nn.functional.linear(torch.randn((3, 64), generator=g).to(torch.bfloat16).to(DEV), odd)
+    assert d.summary()["fallbacks"] == {"disabled": 1, "weight_shape_or_arch": 1}
+    pkg.ops.check_device_status()
