@@ -94,8 +94,10 @@ class LinearDispatch:
 
     # -- the handler ----------------------------------------------------------------
     def register_original_handler(self, fn: Callable) -> None:
-        """`fn(input, weight: Int8Weight, bias)` for calls this dispatch refuses; default:
-        dequantize the weight and run the bf16 linear."""
+        """`fn(input, weight: Int8Weight, bias)`: the host's own handler, called (and
+        counted) for calls this dispatch refuses.  Without one a refused call raises, like
+        every gate of this package: nothing here computes on a silent substitute path.
+        `dequantized_linear` is a ready-made handler."""
         self._original = fn
 
     def _refuse(self, reason: str, inp, weight, bias):
@@ -104,11 +106,10 @@ class LinearDispatch:
         if n == 1 or n % 1000 == 0:
             log.warning("INT8 linear dispatch fallback reason=%s count=%d weight=%s", reason, n,
                         tuple(weight.shape))
-        if self._original is not None:
-            return self._original(inp, weight, bias)
-        x = inp.dequantize() if isinstance(inp, Int8Weight) else inp
-        b = None if bias is None else bias.to(x.dtype)
-        return torch.nn.functional.linear(x, weight.dequantize().to(x.dtype), b)
+        if self._original is None:
+            raise RuntimeError(f"INT8 linear dispatch refused the call ({reason}) and no original "
+                               f"handler is registered")
+        return self._original(inp, weight, bias)
 
     def eligibility(self, inp, weight: Int8Weight) -> str:
         """'eligible' or the first failing condition, in the reference handler's order."""
@@ -146,6 +147,13 @@ class LinearDispatch:
 
     def summary(self) -> dict:
         return {"enabled": self.enabled, "routed": self.routed, "fallbacks": dict(self.fallbacks)}
+
+
+def dequantized_linear(inp, weight: Int8Weight, bias=None):
+    """Original-handler stand-in for hosts without one: dequantize the weight, bf16 linear."""
+    x = inp.dequantize() if isinstance(inp, Int8Weight) else inp
+    b = None if bias is None else bias.to(x.dtype)
+    return torch.nn.functional.linear(x, weight.dequantize().to(x.dtype), b)
 
 
 _default: LinearDispatch | None = None

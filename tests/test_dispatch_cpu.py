@@ -35,6 +35,10 @@ def test_cpu_weight_falls_back_to_the_original_handler_and_is_counted(pkg):
     assert tuple(qw.shape) == (3072, 3072) and qw.dtype == torch.bfloat16
     assert qw.qdata.dtype == torch.int8 and int(qw.qdata.abs().max()) == 127
     assert d.eligibility(x, qw) == "weight_shape_or_arch"
+    with pytest.raises(RuntimeError, match="no original handler"):
+        torch.nn.functional.linear(x, qw, bias)
+    d.fallbacks.clear()
+    d.register_original_handler(pkg.dispatch.dequantized_linear)
     y = torch.nn.functional.linear(x, qw, bias)
     assert torch.equal(y, torch.nn.functional.linear(x, qw.dequantize(), bias))
     assert d.summary() == {"enabled": True, "routed": 0, "fallbacks": {"weight_shape_or_arch": 1}}

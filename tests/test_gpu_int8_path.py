@@ -337,6 +337,7 @@ def test_linear_dispatch_routes_quantized_weights_to_the_int8_path(cuda_pkg, ref
     bias = (torch.randn((3072,), generator=g) * 0.01).to(torch.bfloat16)
     gates = pkg.gates.Gates.all_on()
     d = pkg.dispatch.LinearDispatch(gates=gates)
+    d.register_original_handler(pkg.dispatch.dequantized_linear)
     qw = pkg.dispatch.quantize_weight(w.to(DEV), dispatch=d)
     wq_ref, ws_ref = ref.quantize_weight_per_channel(w)
     assert torch.equal(qw.qdata.cpu(), wq_ref) and torch.equal(bits(qw.scale.cpu()), bits(ws_ref))
