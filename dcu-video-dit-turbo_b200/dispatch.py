@@ -171,7 +171,10 @@ def quantize_weight(weight: torch.Tensor, dispatch: LinearDispatch | None = None
     (scale = absmax/127, round half even, clamp to +-127), as the benchmark's weights are
     prepared."""
     w = weight.float()
-    scale = (w.abs().amax(dim=1) / 127.0).clamp(min=1e-30)
+    absmax = w.abs().amax(dim=1)
+    # tensor / tensor is an IEEE division on every device (a Python-scalar divisor is turned
+    # into a multiplication by its reciprocal on CUDA, which changes the last bit)
+    scale = (absmax / torch.full_like(absmax, 127.0)).clamp(min=1e-30)
     q = torch.clamp(torch.round(w / scale.reshape(-1, 1)), -127, 127).to(torch.int8)
     return Int8Weight(q.contiguous(), scale, dispatch=dispatch)
 

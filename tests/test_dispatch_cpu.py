@@ -34,6 +34,9 @@ def test_cpu_weight_falls_back_to_the_original_handler_and_is_counted(pkg):
     qw = pkg.dispatch.quantize_weight(w, dispatch=d)
     assert tuple(qw.shape) == (3072, 3072) and qw.dtype == torch.bfloat16
     assert qw.qdata.dtype == torch.int8 and int(qw.qdata.abs().max()) == 127
+    from oracle import ref_ops as ref
+    wq_ref, ws_ref = ref.quantize_weight_per_channel(w)
+    assert torch.equal(qw.qdata, wq_ref) and torch.equal(qw.scale, ws_ref)
     assert d.eligibility(x, qw) == "weight_shape_or_arch"
     with pytest.raises(RuntimeError, match="no original handler"):
         torch.nn.functional.linear(x, qw, bias)

@@ -335,6 +335,7 @@ def test_linear_dispatch_routes_quantized_weights_to_the_int8_path(cuda_pkg, ref
     w = (torch.randn((3072, 3072), generator=g) * 0.02).to(torch.bfloat16)
     x = torch.randn((4096, 3072), generator=g).to(torch.bfloat16)
     bias = (torch.randn((3072,), generator=g) * 0.01).to(torch.bfloat16)
+    pkg._lib.admit()     # the freshly built library enters the audit table, as build() does
     gates = pkg.gates.Gates.all_on()
     d = pkg.dispatch.LinearDispatch(gates=gates)
     d.register_original_handler(pkg.dispatch.dequantized_linear)
