@@ -47,9 +47,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
@@ -77,7 +74,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // arithmetic warps, -15%; try_wait with an explicit suspend-time hint of 20 ns to 10 us
 // costs 1.5-5%.)
 constexpr uint32_t kWaitPollLimit = 1u << 26;   // suspending try_wait polls (>= ~1 s)
-constexpr uint32_t kSpinPollLimit = 1u << 27;   // non-suspending test_wait polls (~1-2 s)
 
 __device__ __forceinline__ bool mbar_give_up(volatile int* abort_flag, unsigned int code) {
   atomicOr(&g_device_status, code);
@@ -90,25 +86,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag != 0) break;
-  }
-  return mbar_give_up(abort_flag, code);
-}
-// Low-latency variant for a single waiting thread: spins on the non-suspending
-// mbarrier.test_wait (try_wait may park the thread and wake it late).
-__device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity,
-                                               volatile int* abort_flag, unsigned int code) {
-#pragma unroll 1
-  for (uint32_t i = 0; i < kSpinPollLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((i & 1023u) == 1023u && *abort_flag != 0) break;
   }
   return mbar_give_up(abort_flag, code);
 }
@@ -168,23 +145,6 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// A operand read from tensor memory
-__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 
 // High word of a 128-byte-swizzle shared-memory descriptor with an 8-row-group stride of
 // 1024 bytes: SBO >> 4 = 64 (bits 32-45), version 1 (bits 46-47), swizzle code 2 (61-63).
@@ -193,189 +153,6 @@ constexpr uint32_t kDescHiSw128 = 64u | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
   return ((smem_addr >> 4) & 0x3fffu) | ((lbo_bytes >> 4) << 16);
 }
-
-// Eight back-to-back bf16 MMAs D[tmem] = A.B^T over a 128-wide K extent held as two
-// K-major 128-byte-swizzled half tiles (64 elements each, second half `half_step` 16-byte
-// units after the first): 32 bytes of K per MMA, the first MMA overwrites D.  One asm
-// block, so the issuing thread executes the minimum instruction stream.
-__device__ __forceinline__ void mma_f16_ss_k128(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
-                                                uint32_t idesc, uint32_t half_step) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      ".reg .b64 da, db;\n\t"
-      ".reg .b32 al, bl;\n\t"
-      "setp.ne.b32 p0, 0, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p0;\n\t"
-      "add.u32 al, %1, 2; add.u32 bl, %2, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "add.u32 al, %1, 4; add.u32 bl, %2, 4; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "add.u32 al, %1, 6; add.u32 bl, %2, 6; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "add.u32 al, %1, %5; add.u32 bl, %2, %5; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "add.u32 al, al, 2; add.u32 bl, bl, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "add.u32 al, al, 2; add.u32 bl, bl, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "add.u32 al, al, 2; add.u32 bl, bl, 2; mov.b64 da, {al, %3}; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
-      "}" ::"r"(d_tmem),
-      "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(half_step)
-      : "memory");
-}
-
-// Eight back-to-back bf16 MMAs D[tmem] (+)= A[tmem].B with A read from tensor memory
-// (8 columns = 16 bf16 of K per MMA) and B an MN-major shared-memory operand advancing
-// `b_step` 16-byte units per MMA.  `accumulate` applies to the first MMA only.
-__device__ __forceinline__ void mma_f16_ts_step8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                              uint32_t idesc, uint32_t b_step,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      ".reg .b64 db;\n\t"
-      ".reg .b32 at, bl;\n\t"
-      "setp.ne.b32 p0, %6, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p0;\n\t"
-      "add.u32 at, %1, 8; add.u32 bl, %2, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "add.u32 at, at, 8; add.u32 bl, bl, %5; mov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p1;\n\t"
-      "}" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(b_step), "r"(accumulate)
-      : "memory");
-}
-
-// Eight back-to-back bf16 MMAs from PRE-BUILT 64-bit descriptors: the issuing thread
-// executes one instruction per MMA, so it keeps the tensor pipe fed even when it has to
-// compete for issue slots with busy warps on its scheduler.  The first MMA overwrites D.
-__device__ __forceinline__ void mma_f16_ss_x8(uint32_t d_tmem, const uint64_t (&a)[8],
-                                              const uint64_t (&b)[8], uint32_t idesc) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      "setp.ne.b32 p0, 0, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %9, %17, p0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %17, p1;\n\t"
-      "}" ::"r"(d_tmem),
-      "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]),
-      "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
-      "r"(idesc)
-      : "memory");
-}
-// Same with A read from tensor memory (addresses a[i]); `accumulate` applies to the first.
-__device__ __forceinline__ void mma_f16_ts_x8(uint32_t d_tmem, const uint32_t (&a)[8],
-                                              const uint64_t (&b)[8], uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      "setp.ne.b32 p0, %18, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %9, %17, p0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %10, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %11, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %17, p1;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %17, p1;\n\t"
-      "}" ::"r"(d_tmem),
-      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
-      "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
-      "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Eight back-to-back bf16 MMAs from tables of descriptor LOW words (the high word is the
-// same for every 128-byte-swizzle descriptor): three instructions per MMA and half the
-// registers of full 64-bit tables.  The first MMA overwrites D.
-#define B2_SS_LO(ai, bi, pred)                                                         \
-  "mov.b64 da, {%" #ai ", %17}; mov.b64 db, {%" #bi ", %17};\n\t"                     \
-  "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %18, " pred ";\n\t"
-__device__ __forceinline__ void mma_f16_ss_lo_x8(uint32_t d_tmem, const uint32_t (&a)[8],
-                                                 const uint32_t (&b)[8], uint32_t idesc) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      ".reg .b64 da, db;\n\t"
-      "setp.ne.b32 p0, 0, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t" B2_SS_LO(1, 9, "p0") B2_SS_LO(2, 10, "p1") B2_SS_LO(3, 11, "p1")
-          B2_SS_LO(4, 12, "p1") B2_SS_LO(5, 13, "p1") B2_SS_LO(6, 14, "p1") B2_SS_LO(7, 15, "p1")
-              B2_SS_LO(8, 16, "p1") "}" ::"r"(d_tmem),
-      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
-      "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]),
-      "r"(kDescHiSw128), "r"(idesc)
-      : "memory");
-}
-#undef B2_SS_LO
-// Same with A read from tensor memory (addresses a[i]); `accumulate` applies to the first.
-#define B2_TS_LO(ai, bi, pred)                    \
-  "mov.b64 db, {%" #bi ", %17};\n\t"             \
-  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%" #ai "], db, %18, " pred ";\n\t"
-__device__ __forceinline__ void mma_f16_ts_lo_x8(uint32_t d_tmem, const uint32_t (&a)[8],
-                                                 const uint32_t (&b)[8], uint32_t idesc,
-                                                 uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      ".reg .b64 db;\n\t"
-      "setp.ne.b32 p0, %19, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t" B2_TS_LO(1, 9, "p0") B2_TS_LO(2, 10, "p1") B2_TS_LO(3, 11, "p1")
-          B2_TS_LO(4, 12, "p1") B2_TS_LO(5, 13, "p1") B2_TS_LO(6, 14, "p1") B2_TS_LO(7, 15, "p1")
-              B2_TS_LO(8, 16, "p1") "}" ::"r"(d_tmem),
-      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
-      "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]),
-      "r"(kDescHiSw128), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Four MMAs, same conventions: a[0..3] tensor-memory A addresses, b[0..3] descriptor low words.
-__device__ __forceinline__ void mma_f16_ts_lo_x4(uint32_t d_tmem, const uint32_t* a,
-                                                 const uint32_t* b, uint32_t idesc,
-                                                 uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p0, p1;\n\t"
-      ".reg .b64 db;\n\t"
-      "setp.ne.b32 p0, %11, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "mov.b64 db, {%5, %9};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %10, p0;\n\t"
-      "mov.b64 db, {%6, %9};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], db, %10, p1;\n\t"
-      "mov.b64 db, {%7, %9};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], db, %10, p1;\n\t"
-      "mov.b64 db, {%8, %9};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], db, %10, p1;\n\t"
-      "}" ::"r"(d_tmem),
-      "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]),
-      "r"(kDescHiSw128), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-#undef B2_TS_LO
 
 // Eight / four MMAs whose descriptor low words are `base + compile-time offset`: the adds
 // sit inside the asm block, next to their MMA, so the compiler cannot hoist sixteen
@@ -471,19 +248,6 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
-          taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
-      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
-      "r"(r[30]), "r"(r[31])
       : "memory");
 }
 
