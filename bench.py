@@ -236,7 +236,9 @@ def run_b200(args):
     if world > 1:
         sp = pkg.ulysses.UlyssesSP(splits, HEADS, HEAD_DIM)
     local_heads = HEADS // world
-    chunks = args.head_chunks or (1 if world == 1 else max(1, min(local_heads, 3)))
+    # auto: the most head chunks (all-to-all / attention overlap) whose attention launches
+    # still fill their last wave of SMs
+    chunks = args.head_chunks or (1 if world == 1 else pkg.ulysses.choose_head_chunks(T, local_heads))
     while local_heads % chunks:
         chunks -= 1
     params = pkg.block.make_block_params(HIDDEN, HEADS, HEAD_DIM, FFN, seed=0, device=dev)

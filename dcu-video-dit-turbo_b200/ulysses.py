@@ -28,6 +28,30 @@ def sequence_splits(seq: int, world: int) -> tuple[int, ...]:
     return tuple(base + (1 if r < rem else 0) for r in range(world))
 
 
+def choose_head_chunks(seq: int, local_heads: int, sms: int = 148, q_rows_per_cta: int = 256,
+                       target: float = 0.9, max_chunks: int = 4) -> int:
+    """How many head chunks to split a rank's attention into.
+
+    More chunks hide more of the all-to-all behind attention, but every chunk is its own
+    attention launch of ceil(seq / q_rows_per_cta) * heads_per_chunk CTAs on `sms` SMs, and a
+    launch that fills a fraction of a wave leaves SMs idle (93 CTAs on 148 SMs at 23638
+    tokens and one head per chunk).  Picks the largest divisor of `local_heads` whose
+    launches keep at least `target` of their last wave busy, else the most efficient one;
+    never more than `max_chunks` (the exposed share of the transfer is 1/chunks already)."""
+    ctas_per_head = -(-seq // q_rows_per_cta)
+    best, best_eff = 1, 0.0
+    for chunks in range(min(local_heads, max_chunks), 0, -1):
+        if local_heads % chunks:
+            continue
+        waves = ctas_per_head * (local_heads // chunks) / sms
+        eff = waves / -(-waves // 1)
+        if eff >= target:
+            return chunks
+        if eff > best_eff:
+            best, best_eff = chunks, eff
+    return best
+
+
 class UlyssesSP:
     def __init__(self, splits: Sequence[int], heads: int, dim: int = 128, group=None):
         self.group = group

@@ -193,3 +193,19 @@ def test_flash_gate(pkg, gates):
     assert A.flash_gate(gates, q, k, v, H, None, True, {}, sp1)[1] == "arch"
     gates.flash_enabled = False
     assert A.flash_gate(gates, q, k, v, H, None, True, {}, sp1)[1] == "disabled"
+
+
+def test_head_chunk_choice_fills_the_last_wave():
+    """23638 tokens give 93 CTAs per head: one head per launch would leave 55 of 148 SMs idle,
+    so fewer, larger chunks are chosen; 109099 tokens (427 CTAs per head) keep the most chunks."""
+    import importlib
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    ul = importlib.import_module("dcu-video-dit-turbo_b200").ulysses
+    assert [ul.choose_head_chunks(23638, 24 // p) for p in (2, 4, 8)] == [4, 2, 1]
+    assert [ul.choose_head_chunks(109099, 24 // p) for p in (2, 4, 8)] == [4, 3, 3]
+    assert ul.choose_head_chunks(100, 3) in (1, 3)       # tiny launches: any divisor, never 0
+    for heads in (1, 2, 3, 6, 12, 24):
+        c = ul.choose_head_chunks(5000, heads)
+        assert 1 <= c <= 4 and heads % c == 0
