@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory FROM THE REFERENCE'S OWN PYTHON.
 
-Run once in a container that has the reference checkout (default /root/reference,
-or REFERENCE_ROOT); the fixtures are committed, this script documents how they were
+Run once where the reference checkout is available (REFERENCE_ROOT=<path to it>
+python make_golden.py); the fixtures are committed, this script documents how they were
 made and can regenerate them.  Nothing else reads the reference tree.
 
 What is extracted (by `ast`, the way the reference's own contract verifier does in
@@ -28,7 +28,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ["REFERENCE_ROOT"])   # path of the reference checkout
 OUT = Path(__file__).resolve().parent
 
 
