@@ -47,9 +47,11 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--head-chunks", type=int, default=0, help="0 = auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fuse-residual", action="store_true",
+                    help="gated residuals as their own kernel instead of in the GEMM epilogue")
     ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the 12 kernels one by one")
     ap.add_argument("--kernel", default=None,
-                    choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant",
+                    choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant", "rope_pack", "quant_gathered", "gemm_out_residual",
                              "epilogue", "gate", "rope"],
                     help="time ONE kernel alone on the block's shapes instead of the block")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
@@ -242,7 +244,8 @@ def run_b200(args):
     while local_heads % chunks:
         chunks -= 1
     params = pkg.block.make_block_params(HIDDEN, HEADS, HEAD_DIM, FFN, seed=0, device=dev)
-    blk = pkg.block.DiTBlock(params, sp=sp, head_chunks=chunks, overlap=True)
+    blk = pkg.block.DiTBlock(params, sp=sp, head_chunks=chunks, overlap=True,
+                             fuse_residual=not args.no_fuse_residual)
     cos_all, sin_all = pkg.block.rope_tables(pkg.block.grid_positions(T))
     cos, sin = cos_all[row0:row0 + L].to(dev), sin_all[row0:row0 + L].to(dev)
     g = torch.Generator().manual_seed(1234 + rank)
@@ -448,6 +451,13 @@ def run_kernel(args):
         views = [tuple(b[:, i].transpose(0, 1).unsqueeze(0) for i in range(3)) for b in bufs]
         fn = lambda i: ops.fwd_bhsd(*views[i % 2], HEAD_DIM ** -0.5)
         work, unit, peak, bound = 4.0 * T * T * HEADS * HEAD_DIM, "TFLOP/s", pk["bf16_burst"], "tensor"
+    elif name == "gemm_out_residual":   # out-projection with the gated residual in its epilogue
+        k, n = HIDDEN, HIDDEN
+        a, w = ri8(T, k), ri8(n, k)
+        rs, cs, b, gate = torch.rand(T, device=dev), torch.rand(n, device=dev) * 1e-4, vec(n), vec(n)
+        xs = [rnd(T, n) for _ in range(nbuf(T * n * 2))]
+        fn = lambda i: ops.int8_gemm_dequant_residual_(xs[i % len(xs)], gate, a, rs, w, cs, b)
+        work, unit, peak, bound = 2.0 * T * n * k, "TOP/s", 2 * pk["bf16_burst"], "tensor"
     elif name.startswith("gemm"):
         k, n = {"gemm_qkv": (HIDDEN, 3 * HIDDEN), "gemm_fc1": (HIDDEN, 2 * FFN), "gemm_c1": (HIDDEN, HIDDEN)}[name]
         a, w = ri8(T, k), ri8(n, k)
@@ -482,6 +492,16 @@ def run_kernel(args):
         rs, cs = torch.rand(T, device=dev), torch.rand(n, device=dev)
         fn = lambda i: ops.epilogue_vec4(accs[i % len(accs)], rs, cs)
         work, unit, peak, bound = T * n * 6 + T * 4 + n * 4, "GB/s", pk["hbm_gbs"], "hbm"
+    elif name == "rope_pack":   # norm + rotary writing the all-to-all send buffer (8 ranks, 3 chunks)
+        bufs = [rnd(T, 3, HEADS, HEAD_DIM) for _ in range(nbuf(T * 3 * HIDDEN * 2))]
+        cos, sin = pkg.block.rope_tables(pkg.block.grid_positions(T))
+        cos, sin, w = cos.to(dev), sin.to(dev), vec(HEAD_DIM) + 1
+        fn = lambda i: ops.qk_norm_rope_pack(bufs[i % len(bufs)], w, w, cos, sin, 8, 3)
+        work, unit, peak, bound = T * 3 * HIDDEN * 4 + T * 64 * 8, "GB/s", pk["hbm_gbs"], "hbm"
+    elif name == "quant_gathered":   # quantizer reading the reverse all-to-all layout (8 ranks, 3 chunks)
+        xs = [rnd(3, 8, T, HIDDEN // 24) for _ in range(nbuf(T * HIDDEN * 2))]
+        fn = lambda i: ops.quantize_int8_rowwise_gathered(xs[i % len(xs)])
+        work, unit, peak, bound = T * HIDDEN * 3 + T * 4, "GB/s", pk["hbm_gbs"], "hbm"
     else:  # rope
         bufs = [rnd(T, 3, HEADS, HEAD_DIM) for _ in range(nbuf(T * 3 * HIDDEN * 2))]
         cos, sin = pkg.block.rope_tables(pkg.block.grid_positions(T))

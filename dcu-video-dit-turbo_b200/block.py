@@ -71,8 +71,9 @@ def grid_positions(tokens: int, height: int = 22, width: int = 38) -> torch.Tens
 
 class DiTBlock:
     def __init__(self, params: dict, sp: UlyssesSP | None = None, head_chunks: int = 1,
-                 overlap: bool = True):
+                 overlap: bool = True, fuse_residual: bool = True):
         self.p = params
+        self.fuse_residual = fuse_residual   # gated residuals in the GEMM epilogue (same bits either way)
         self.sp = sp
         self.head_chunks = head_chunks
         self.overlap = overlap
@@ -91,6 +92,13 @@ class DiTBlock:
             return out.transpose(1, 2).reshape(L, self.heads * self.head_dim)
         o = self.sp.attention_fused(qkv, self._attn, chunks=self.head_chunks, overlap=self.overlap)
         return o.reshape(L, self.heads * self.head_dim)
+
+    def _linear_residual(self, x, gate, q8, s, wq, ws, bias) -> None:
+        """x += gate * linear(q8): one kernel, or GEMM + gate-residual kernel."""
+        if self.fuse_residual:
+            ops.int8_gemm_dequant_residual_(x, gate, q8, s.view(-1), wq, ws, bias)
+        else:
+            ops.gate_residual_(x, ops.int8_gemm_dequant(q8, s.view(-1), wq, ws, bias), gate)
 
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         """x bf16 [L, C] (this rank's tokens); cos/sin fp32 [L, 64] for the same rows.
@@ -111,11 +119,11 @@ class DiTBlock:
         else:
             ops.qk_norm_rope_(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin)
             q8, s = ops.quantize_int8_rowwise(self.attention(qkv))
-        ops.int8_gemm_dequant_residual_(x, p["gate1"], q8, s.view(-1), p["wq_out"], p["ws_out"], p["b_out"])
+        self._linear_residual(x, p["gate1"], q8, s, p["wq_out"], p["ws_out"], p["b_out"])
         q8, s = ops.layernorm_mod_quant(x, p["scale2"], p["shift2"])
         f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])
         q8, s = ops.swiglu_quantize_int8_rowwise(f)
-        ops.int8_gemm_dequant_residual_(x, p["gate2"], q8, s.view(-1), p["wq_fc2"], p["ws_fc2"], p["b_fc2"])
+        self._linear_residual(x, p["gate2"], q8, s, p["wq_fc2"], p["ws_fc2"], p["b_fc2"])
         return x
 
 

@@ -49,6 +49,17 @@ __device__ __forceinline__ void epilogue_stage_columns(const EpilogueArgs& a, fl
   }
 }
 
+// Residual mode reads x[row, col0 .. col0+256) in 16-byte pieces, one row per thread: every
+// piece would be a fresh trip to DRAM in the middle of the epilogue.  The row segment (four
+// 128-byte lines) is requested into L2 while the tile's main loop is still running.
+__device__ __forceinline__ void epilogue_prefetch_residual(const EpilogueArgs& a, int row, int col0) {
+  if (a.gate == nullptr || row >= a.M) return;
+  const char* p = reinterpret_cast<const char*>(a.residual + (int64_t)row * a.N + col0);
+#pragma unroll
+  for (int b = 0; b < kEpiTileN * 2; b += 128)
+    if (col0 + b / 2 < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + b));
+}
+
 // One 32-column chunk of one row.  `c` is the chunk's offset inside the tile, `col` its
 // global column; the row is valid and col < N (checked by the caller).
 __device__ __forceinline__ void epilogue_store_chunk(const EpilogueArgs& a, const uint32_t (&v)[32],

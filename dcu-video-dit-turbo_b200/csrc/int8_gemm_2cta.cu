@@ -235,13 +235,14 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       decode_tile(tile, args, m_idx, n_idx);
       const int col0 = n_idx * BN;
       float* cvec = colvec + buf * kColVecFloats;
+      const int row = m_idx * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       if (fused) {
+        epilogue_prefetch_residual(epi, row, col0);
         epilogue_stage_columns(epi, cvec, col0, et);
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
       if (!mbar_wait(tfull0 + buf * 8, buf_phase, abort_flag, kStatusGemmTimeout)) break;
       tc_fence_after();
-      const int row = m_idx * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const bool row_ok = row < epi.M;
       const float rsv = (fused && row_ok) ? epi.rs[row] : 0.f;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);

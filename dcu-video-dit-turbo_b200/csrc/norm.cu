@@ -222,7 +222,14 @@ qk_norm_rope_pack_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ send
     const int seg = h / c_heads, ci = h - seg * c_heads;     // seg = p*chunks + ch
     const int p = seg / chunks, ch = seg - p * chunks;
     uint4* dst = send + (((((int64_t)ch * world + p) * L + s) * c_heads + ci) * 3 + part) * 16 + l;
-    // every lane takes part in the shuffles; V lanes discard the result
+    // V is a plain copy.  The 16 threads of a (row, part, head) group agree on `part`, and the
+    // shuffles below stay inside such a group and name only its 16 lanes, so a V group can
+    // leave while the other half of the warp (a Q or K group when H is odd) carries on.
+    const uint32_t group_mask = 0xffffu << (threadIdx.x & 16);
+    if (part == 2) {
+      if (live) *dst = v;
+      continue;
+    }
     const uint4 wv = (part == 1 ? kw : qw)[l];
     const uint32_t w[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
     float e[8];
@@ -234,7 +241,7 @@ qk_norm_rope_pack_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ send
       ss += e[2 * j] * e[2 * j] + e[2 * j + 1] * e[2 * j + 1];
     }
 #pragma unroll
-    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(group_mask, ss, off);
     const float rms = rsqrtf(ss * (1.0f / 128.0f) + eps);
     const float4 c = cos_tab[s * 16 + l], sn = sin_tab[s * 16 + l];
     const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
@@ -245,7 +252,7 @@ qk_norm_rope_pack_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ send
       const float y1 = e[2 * j + 1] * rms * bf16hi_to_f32(ww[j]);
       o[j] = pack_bf16x2_rn(y0 * cc[j] - y1 * sv[j], y1 * cc[j] + y0 * sv[j]);
     }
-    if (live) *dst = part == 2 ? v : make_uint4(o[0], o[1], o[2], o[3]);
+    if (live) *dst = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 

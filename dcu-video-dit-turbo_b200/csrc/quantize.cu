@@ -46,11 +46,13 @@ struct RowGather {
   int chunks;
   int world;
 };
-__device__ __forceinline__ int64_t source_vec(const RowGather& g, int64_t row, int64_t M, int kvec, int c) {
-  if (g.seg_vec == 0) return row * kvec + c;
+// Offset of row 0's vector c, and the distance between consecutive rows: the segment
+// arithmetic (two integer divisions) runs once per thread, outside the row loop.
+__device__ __forceinline__ int64_t source_vec0(const RowGather& g, int64_t M, int c) {
+  if (g.seg_vec == 0) return c;
   const int seg = c / g.seg_vec, w = c - seg * g.seg_vec;
   const int p = seg / g.chunks, ch = seg - p * g.chunks;
-  return (((int64_t)ch * g.world + p) * M + row) * g.seg_vec + w;
+  return ((int64_t)ch * g.world + p) * M * g.seg_vec + w;
 }
 
 // One row per TPR threads, VPT 16-byte vectors (8 bf16) per thread, K % 8 == 0,
@@ -64,6 +66,13 @@ quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* 
   constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
   const int slot = threadIdx.x / TPR;
   const int lane = threadIdx.x % TPR;
+  const int64_t row_step = gather.seg_vec == 0 ? kvec : gather.seg_vec;
+  int64_t src0[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = lane + i * TPR;
+    src0[i] = c < kvec ? source_vec0(gather, M, c) : 0;
+  }
   for (int64_t row0 = (int64_t)blockIdx.x * RPC; row0 < M; row0 += (int64_t)gridDim.x * RPC) {
     const int64_t row = row0 + slot;
     const bool live = row < M;
@@ -71,8 +80,7 @@ quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* 
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + i * TPR;
-      v[i] = (live && c < kvec) ? ldg_stream(x + source_vec(gather, row, M, kvec, c))
-                                : make_uint4(0, 0, 0, 0);
+      v[i] = (live && c < kvec) ? ldg_stream(x + src0[i] + row * row_step) : make_uint4(0, 0, 0, 0);
     }
     uint32_t acc = 0;
 #pragma unroll
