@@ -49,9 +49,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-residual", action="store_true",
                     help="gated residuals as their own kernel instead of in the GEMM epilogue")
-    ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the 12 kernels one by one")
+    ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the kernels one by one")
     ap.add_argument("--kernel", default=None,
-                    choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant", "rope_pack", "quant_gathered", "gemm_out_residual",
+                    choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant", "rope_pack", "quant_gathered", "gemm_out_residual", "gemm_fc2", "gemm_fc2_residual",
                              "epilogue", "gate", "rope"],
                     help="time ONE kernel alone on the block's shapes instead of the block")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
@@ -284,7 +284,7 @@ def run_b200(args):
         y = blk.forward(x_dev, cos, sin)
     ops.check_device_status(dev)
     attn_events.clear()
-    # single GPU: the pass is replayed from a CUDA graph (one launch instead of twelve);
+    # single GPU: the pass is replayed from a CUDA graph (one launch instead of eleven);
     # the attention events are recorded inside the captured pass by a second, eager run
     use_graph = world == 1 and not args.no_graph
     run_step = lambda xin: blk.forward(xin, cos, sin)
@@ -451,15 +451,16 @@ def run_kernel(args):
         views = [tuple(b[:, i].transpose(0, 1).unsqueeze(0) for i in range(3)) for b in bufs]
         fn = lambda i: ops.fwd_bhsd(*views[i % 2], HEAD_DIM ** -0.5)
         work, unit, peak, bound = 4.0 * T * T * HEADS * HEAD_DIM, "TFLOP/s", pk["bf16_burst"], "tensor"
-    elif name == "gemm_out_residual":   # out-projection with the gated residual in its epilogue
-        k, n = HIDDEN, HIDDEN
+    elif name in ("gemm_out_residual", "gemm_fc2_residual"):   # GEMM with the gated residual in its epilogue
+        k, n = (HIDDEN, HIDDEN) if name == "gemm_out_residual" else (FFN, HIDDEN)
         a, w = ri8(T, k), ri8(n, k)
         rs, cs, b, gate = torch.rand(T, device=dev), torch.rand(n, device=dev) * 1e-4, vec(n), vec(n)
         xs = [rnd(T, n) for _ in range(nbuf(T * n * 2))]
         fn = lambda i: ops.int8_gemm_dequant_residual_(xs[i % len(xs)], gate, a, rs, w, cs, b)
         work, unit, peak, bound = 2.0 * T * n * k, "TOP/s", 2 * pk["bf16_burst"], "tensor"
     elif name.startswith("gemm"):
-        k, n = {"gemm_qkv": (HIDDEN, 3 * HIDDEN), "gemm_fc1": (HIDDEN, 2 * FFN), "gemm_c1": (HIDDEN, HIDDEN)}[name]
+        k, n = {"gemm_qkv": (HIDDEN, 3 * HIDDEN), "gemm_fc1": (HIDDEN, 2 * FFN), "gemm_c1": (HIDDEN, HIDDEN),
+                "gemm_fc2": (FFN, HIDDEN)}[name]
         a, w = ri8(T, k), ri8(n, k)
         rs, cs, b = torch.rand(T, device=dev), torch.rand(n, device=dev), vec(n)
         fn = lambda i: ops.int8_gemm_dequant(a, rs, w, cs, b)
