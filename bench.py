@@ -51,7 +51,7 @@ def parse():
                     help="gated residuals as their own kernel instead of in the GEMM epilogue")
     ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the kernels one by one")
     ap.add_argument("--kernel", default=None,
-                    choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant", "rope_pack", "quant_gathered", "gemm_out_residual", "gemm_fc2", "gemm_fc2_residual",
+                    choices=["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant", "rope_pack", "quant_gathered", "gemm_out_residual", "gemm_fc2", "gemm_fc2_residual", "frames_u8",
                              "epilogue", "gate", "rope"],
                     help="time ONE kernel alone on the block's shapes instead of the block")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
@@ -493,6 +493,11 @@ def run_kernel(args):
         rs, cs = torch.rand(T, device=dev), torch.rand(n, device=dev)
         fn = lambda i: ops.epilogue_vec4(accs[i % len(accs)], rs, cs)
         work, unit, peak, bound = T * n * 6 + T * 4 + n * 4, "GB/s", pk["hbm_gbs"], "hbm"
+    elif name == "frames_u8":   # 121 decoded frames 704x1280 RGB fp32 -> bytes (`--tokens` is ignored)
+        n = 121 * 704 * 1280 * 3
+        xs = [torch.rand((121, 704, 1280, 3), device=dev, generator=gen) for _ in range(2)]
+        fn = lambda i: ops.images_to_u8(xs[i % 2])
+        work, unit, peak, bound = n * 5, "GB/s", pk["hbm_gbs"], "hbm"
     elif name == "rope_pack":   # norm + rotary writing the all-to-all send buffer (8 ranks, 3 chunks)
         bufs = [rnd(T, 3, HEADS, HEAD_DIM) for _ in range(nbuf(T * 3 * HIDDEN * 2))]
         cos, sin = pkg.block.rope_tables(pkg.block.grid_positions(T))

@@ -42,6 +42,7 @@ SYMBOLS = {
     "b2_qk_norm_rope": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp]),
     "b2_qk_norm_rope_pack": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
     "b2_quantize_int8_rowwise_gathered": (_int, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "b2_images_to_u8": (_int, [_vp, _i32, _vp, _i64, _vp]),
     "b2_gate_residual": (_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
 }
 

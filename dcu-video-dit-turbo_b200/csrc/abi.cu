@@ -138,6 +138,14 @@ int b2_mod_scale_shift(void* x, const void* scale, const void* shift, int64_t M,
   return launch_mod_scale_shift(x, scale, shift, M, C, (cudaStream_t)stream);
 }
 
+int b2_images_to_u8(const void* images, int32_t dtype, uint8_t* out, int64_t n, void* stream) {
+  if (n < 0) return fail(B2_BAD_SHAPE, "images_to_u8: negative size");
+  if (dtype < 0 || dtype > 2) return fail(B2_BAD_DTYPE, "images_to_u8: dtype must be 0 (float32), 1 (bfloat16) or 2 (float16)");
+  if (n == 0) return B2_OK;
+  if (!images || !out) return fail(B2_NULL_POINTER, "images_to_u8: null pointer");
+  return launch_images_to_u8(images, dtype, out, n, (cudaStream_t)stream);
+}
+
 int b2_gate_residual(void* x, const void* y, const void* gate, int64_t M, int64_t C, void* stream) {
   if (M < 0 || C < 0) return fail(B2_BAD_SHAPE, "gate_residual: negative size");
   if (M == 0 || C == 0) return B2_OK;

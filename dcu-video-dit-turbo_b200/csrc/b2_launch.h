@@ -18,6 +18,7 @@ int launch_epilogue(const int32_t* acc, const float* rs, const float* cs, const 
                     int bias_kind, void* out, int64_t M, int64_t N, cudaStream_t stream);
 int launch_mod_scale_shift(void* x, const void* scale, const void* shift, int64_t M, int64_t C,
                            cudaStream_t stream);
+int launch_images_to_u8(const void* x, int dtype, uint8_t* out, int64_t n, cudaStream_t stream);
 int launch_gate_residual(void* x, const void* y, const void* gate, int64_t M, int64_t C,
                          cudaStream_t stream);
 int launch_layernorm_mod(const void* x, const void* scale, const void* shift, void* out_bf16,

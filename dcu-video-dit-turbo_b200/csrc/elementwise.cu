@@ -10,6 +10,8 @@
 //   kernels/int8-epilogue/epilogue_kernel.hip:39-53      (reference)
 //   kernels/int8-epilogue-vec4/epilogue_kernel.hip:17-30 (reference)
 //   kernels/mod-scale-shift/mod_kernel.hip:16-21         (reference)
+#include <cuda_fp16.h>
+
 #include "b2_common.cuh"
 
 namespace b2 {
@@ -252,6 +254,107 @@ int launch_mod_scale_shift(void* x, const void* scale, const void* shift, int64_
         (__nv_bfloat16*)x, (const __nv_bfloat16*)scale, (const __nv_bfloat16*)shift, M, C);
   }
   return check_launch("mod_scale_shift");
+}
+
+// ---- decoded frames -> RGB24 bytes ------------------------------------------------------
+// out = uint8(clamp(x * 255, 0, 255)) with the product rounded to the input's own type and
+// the cast truncating, i.e. the host's `(images * 255).clamp(0, 255).byte()` over a whole
+// video in one launch (launcher/benchmark_launcher_v14_hires_int8_candidate.py:645-647 in the
+// reference).  NaN gives 0.  DT: 0 = fp32, 1 = bf16, 2 = fp16.
+template <int DT>
+__device__ __forceinline__ uint32_t frame_byte(float v) {
+  float p = __fmul_rn(v, 255.0f);
+  if (DT == 1) p = round_bf16_f32(p);
+  if (DT == 2) p = __half2float(__float2half_rn(p));
+  p = fminf(fmaxf(p, 0.0f), 255.0f);          // fmaxf/fminf drop a NaN operand: NaN -> 0
+  return (uint32_t)__float2int_rz(p);
+}
+template <int DT>
+__device__ __forceinline__ float frame_load(const void* x, int64_t i) {
+  if (DT == 0) return reinterpret_cast<const float*>(x)[i];
+  if (DT == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+  return __half2float(reinterpret_cast<const __half*>(x)[i]);
+}
+// Every load and store instruction of a warp covers one contiguous run (512 bytes in, 128 or
+// 256 bytes out): lane l of iteration k handles vector (k*32 + l) of the warp's block, four
+// independent loads in flight per thread.
+template <int DT>
+__global__ void __launch_bounds__(256) images_to_u8_kernel(const void* __restrict__ x, uint8_t* __restrict__ out,
+                                                           int64_t n) {
+  constexpr int EPV = DT == 0 ? 4 : 8;            // elements per 16-byte vector
+  constexpr int kUnroll = 4;
+  const int64_t vecs = n / EPV;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t v0 = warp * (32 * kUnroll); v0 < vecs; v0 += warps * (32 * kUnroll)) {
+    uint4 q[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      const int64_t v = v0 + k * 32 + lane;
+      q[k] = v < vecs ? ldg_stream(reinterpret_cast<const uint4*>(x) + v) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      const int64_t v = v0 + k * 32 + lane;
+      if (v >= vecs) continue;
+      const uint32_t h[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+      if (DT == 0) {
+        reinterpret_cast<uint32_t*>(out)[v] =
+            frame_byte<DT>(__uint_as_float(h[0])) | (frame_byte<DT>(__uint_as_float(h[1])) << 8) |
+            (frame_byte<DT>(__uint_as_float(h[2])) << 16) | (frame_byte<DT>(__uint_as_float(h[3])) << 24);
+      } else {
+        uint32_t w[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float e[4];
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            const uint32_t pr = h[2 * j + m];
+            if (DT == 1) {
+              e[2 * m] = bf16lo_to_f32(pr);
+              e[2 * m + 1] = bf16hi_to_f32(pr);
+            } else {
+              const __half2 hh = *reinterpret_cast<const __half2*>(&pr);
+              e[2 * m] = __low2float(hh);
+              e[2 * m + 1] = __high2float(hh);
+            }
+          }
+          w[j] = frame_byte<DT>(e[0]) | (frame_byte<DT>(e[1]) << 8) | (frame_byte<DT>(e[2]) << 16) |
+                 (frame_byte<DT>(e[3]) << 24);
+        }
+        reinterpret_cast<uint2*>(out)[v] = make_uint2(w[0], w[1]);
+      }
+    }
+  }
+  // tail (n % EPV elements): scalar
+  for (int64_t i = vecs * EPV + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = (uint8_t)frame_byte<DT>(frame_load<DT>(x, i));
+}
+template <int DT>
+__global__ void __launch_bounds__(256) images_to_u8_scalar_kernel(const void* __restrict__ x,
+                                                                  uint8_t* __restrict__ out, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = (uint8_t)frame_byte<DT>(frame_load<DT>(x, i));
+}
+
+int launch_images_to_u8(const void* x, int dtype, uint8_t* out, int64_t n, cudaStream_t stream) {
+  const bool vec = aligned16(x) && aligned16(out);
+  int64_t blocks = (n / 64 + 255) / 256;
+  const int64_t cap = (int64_t)kNumSMsB200 * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+#define B2_U8(DT)                                                                                    \
+  do {                                                                                               \
+    if (vec) images_to_u8_kernel<DT><<<(int)blocks, 256, 0, stream>>>(x, out, n);                    \
+    else images_to_u8_scalar_kernel<DT><<<(int)cap, 256, 0, stream>>>(x, out, n);                    \
+  } while (0)
+  if (dtype == 0) B2_U8(0);
+  else if (dtype == 1) B2_U8(1);
+  else B2_U8(2);
+#undef B2_U8
+  return check_launch("images_to_u8");
 }
 
 int launch_gate_residual(void* x, const void* y, const void* gate, int64_t M, int64_t C,

@@ -390,6 +390,22 @@ def quantize_int8_rowwise_gathered(x: torch.Tensor):
     return [q, s]
 
 
+_FRAME_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def images_to_u8(images: torch.Tensor) -> torch.Tensor:
+    """Decoded frames (any shape, fp32 / bf16 / fp16, values nominally in [0,1]) -> uint8 of
+    the same shape: `(images * 255).clamp(0, 255).byte()` for the whole clip in one launch
+    (NaN -> 0)."""
+    _require(images.is_cuda and images.is_contiguous(), "images must be a contiguous CUDA tensor")
+    _require(images.dtype in _FRAME_DTYPES, "images must be float32, bfloat16 or float16")
+    out = torch.empty(images.shape, dtype=torch.uint8, device=images.device)
+    if images.numel():
+        _call("b2_images_to_u8", images, images.data_ptr(), _FRAME_DTYPES[images.dtype], out.data_ptr(),
+              images.numel(), _stream(images))
+    return out
+
+
 def gate_residual_(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     """In place x = bf16(x + bf16(gate*y)); returns x."""
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()

@@ -192,6 +192,13 @@ int b2_qk_norm_rope_pack(const void* qkv_bf16, void* send_bf16, const void* q_we
 int b2_quantize_int8_rowwise_gathered(const void* x_bf16, int8_t* q, float* scale, int64_t M,
                                       int64_t K, int32_t world, int32_t chunks, void* stream);
 
+/* Decoded frames -> RGB24 bytes for the video encoder, the whole clip in one launch:
+ * out[i] = uint8(clamp(images[i] * 255, 0, 255)), product rounded to the input type, cast
+ * truncating, NaN -> 0.  Replaces the per-frame `(image * 255).clamp(0, 255).byte()` + copy
+ * that the reference batches in launcher/benchmark_launcher_v14_hires_int8_candidate.py:607-723
+ * (H3_SAVE_BATCH_U8).  dtype: 0 float32, 1 bfloat16, 2 float16; n = element count. */
+int b2_images_to_u8(const void* images, int32_t dtype, uint8_t* out, int64_t n, void* stream);
+
 /* x = bf16(x + bf16(gate[c]*y)) in place on x; x,y bf16 [M,C], gate bf16 [C]. */
 int b2_gate_residual(void* x_bf16, const void* y_bf16, const void* gate_bf16, int64_t M, int64_t C,
                      void* stream);

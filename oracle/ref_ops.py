@@ -263,6 +263,15 @@ def unpack_gathered(recv: torch.Tensor) -> torch.Tensor:
     return recv.permute(2, 1, 0, 3, 4).reshape(L, world * chunks * c * d).contiguous()
 
 
+def images_to_u8(images: torch.Tensor) -> torch.Tensor:
+    """`(images * 255).clamp(0, 255).byte()`, the expression the reference batches over a
+    whole clip (launcher/benchmark_launcher_v14_hires_int8_candidate.py:645-647); the product
+    keeps the input dtype, the cast truncates.  NaN (undefined in that cast) is defined as 0."""
+    prod = images * 255
+    prod = torch.where(torch.isnan(prod), torch.zeros_like(prod), prod)
+    return prod.clamp(0, 255).to(torch.uint8)
+
+
 # ----------------------------------------------------------------------------
 # DiT block glue.  No reference source exists for these (they live in ComfyUI's
 # model file, which is not part of the reference tree): PARITY UNPINNED.  The

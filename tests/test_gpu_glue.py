@@ -100,3 +100,39 @@ def test_gate_residual_bit_exact(cuda_pkg, ref, m, c):
     xd = x.to(DEV)
     cuda_pkg.ops.gate_residual_(xd, y.to(DEV), gate.to(DEV))
     assert torch.equal(bits(xd.cpu()), bits(ref.gate_residual(x, y, gate)))
+
+
+@pytest.mark.parametrize("shape", [(3, 17, 23, 3), (1, 1, 1, 3), (2, 64, 64, 3), (5, 7, 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_images_to_u8_bit_exact(cuda_pkg, ref, shape, dtype):
+    """One launch over the clip == the oracle == the per-frame expression evaluated by torch on
+    the device; special values follow the documented rule (NaN -> 0)."""
+    g = torch.Generator().manual_seed(sum(shape))
+    x = (torch.rand(shape, generator=g) * 1.5 - 0.25).to(dtype)
+    flat = x.view(-1)
+    vals = torch.tensor([0.0, 1.0, 1 / 255, 254.5 / 255, -1e-8, 2.0]).to(dtype)
+    k = min(6, flat.numel())
+    flat[:k] = vals[:k]
+    got = cuda_pkg.ops.images_to_u8(x.to(DEV))
+    assert got.dtype == torch.uint8 and got.shape == x.shape
+    assert torch.equal(got.cpu(), ref.images_to_u8(x))
+    assert torch.equal(got, (x.to(DEV) * 255).clamp(0, 255).byte())
+    special = torch.tensor([float("nan"), float("inf"), -float("inf"), 0.5] * 5).to(dtype)
+    assert cuda_pkg.ops.images_to_u8(special.to(DEV)).cpu().tolist() == [0, 255, 0, 127] * 5
+    # an unaligned view takes the scalar kernel
+    y = x.reshape(-1)[1:]
+    if y.numel():
+        assert torch.equal(cuda_pkg.ops.images_to_u8(y.to(DEV).clone()).cpu(), ref.images_to_u8(y))
+    with pytest.raises(RuntimeError):
+        cuda_pkg.ops.images_to_u8(x.to(DEV).to(torch.float64))
+
+
+def test_batched_save_returns_the_per_frame_bytes(cuda_pkg, ref):
+    s = cuda_pkg.save.BatchU8Save(enabled=True)
+    g = torch.Generator().manual_seed(9)
+    clip = torch.rand((4, 36, 64, 3), generator=g)
+    host = s.frames_u8(clip.to(DEV), bit_depth=8)
+    assert not host.is_cuda and host.is_pinned() and s.hits == 1
+    per_frame = torch.stack([(f * 255).clamp(0, 255).byte() for f in clip])
+    assert torch.equal(host, per_frame)
+    cuda_pkg.ops.check_device_status()
