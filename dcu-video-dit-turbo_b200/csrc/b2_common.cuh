@@ -29,6 +29,17 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
 }
+// Packed bf16 product and sum, each rounded once to nearest even (subnormals kept).
+__device__ __forceinline__ uint32_t bf16x2_mul_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_add_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ float round_bf16_f32(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }

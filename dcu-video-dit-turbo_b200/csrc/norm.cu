@@ -127,11 +127,12 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
         for (int j = 0; j < 4; ++j) {
           const uint32_t n = pack_bf16x2_rn((bf16lo_to_f32(w[j]) - mean) * rstd,
                                             (bf16hi_to_f32(w[j]) - mean) * rstd);
-          const float f0 = bf16lo_to_f32(fcw[j]), f1 = bf16hi_to_f32(fcw[j]);
-          const uint32_t p = pack_bf16x2_rn(__fmul_rn(bf16lo_to_f32(n), f0),
-                                            __fmul_rn(bf16hi_to_f32(n), f1));
-          w[j] = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(p), bf16lo_to_f32(shw[j])),
-                                __fadd_rn(bf16hi_to_f32(p), bf16hi_to_f32(shw[j])));
+          // The two modulation roundings as packed bf16 instructions on the FMA pipe.  Each is
+          // the correctly rounded product / sum of two bf16 values, which is what the fp32
+          // formulation computes too: the fp32 product of two bf16 is exact, and the fp32 sum
+          // of two bf16 is exact unless their exponents lie more than 16 apart, where the small
+          // term is far below half an ulp in either formulation.
+          w[j] = bf16x2_add_rn(bf16x2_mul_rn(n, fcw[j]), shw[j]);
           if (QUANT) acc = absmax_bf16x2(acc, w[j]);
         }
         v[i] = make_uint4(w[0], w[1], w[2], w[3]);

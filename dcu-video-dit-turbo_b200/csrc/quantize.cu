@@ -180,9 +180,9 @@ __device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
     s0 = silu_exact(g0);
     s1 = silu_exact(g1);
   }
-  const uint32_t s = pack_bf16x2_rn(s0, s1);
-  return pack_bf16x2_rn(__fmul_rn(bf16lo_to_f32(s), bf16lo_to_f32(u)),
-                        __fmul_rn(bf16hi_to_f32(s), bf16hi_to_f32(u)));
+  // second rounding: the fp32 product of two bf16 values is exact, so rounding it to bf16 is
+  // the packed bf16 multiply's single rounding (one FMA-pipe instruction instead of seven)
+  return bf16x2_mul_rn(pack_bf16x2_rn(s0, s1), u);
 }
 
 template <int TPR, int VPT>
