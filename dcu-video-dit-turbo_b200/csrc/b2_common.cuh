@@ -94,8 +94,9 @@ __device__ __forceinline__ uint32_t quant_pair(uint32_t w, float r) {
   float d0 = __fmul_rn(bf16lo_to_f32(w), r);
   float d1 = __fmul_rn(bf16hi_to_f32(w), r);
   uint32_t p = pack_bf16x2_rn(d0, d1);
-  float e0 = fminf(bf16lo_to_f32(p), 127.0f);
-  float e1 = fminf(bf16hi_to_f32(p), 127.0f);
+  asm("min.bf16x2 %0, %0, %1;" : "+r"(p) : "r"(0x42fe42feu));  // both halves: min(d, 127.0)
+  float e0 = bf16lo_to_f32(p);
+  float e1 = bf16hi_to_f32(p);
   // adding 1.5*2^23 rounds to nearest-even integer; the low mantissa byte is the
   // two's-complement int8
   uint32_t b0 = __float_as_uint(__fadd_rn(e0, 12582912.0f));
