@@ -93,12 +93,18 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
       const int c = lane + i * TPR;
       v[i] = (live && c < cvec) ? ldg_stream(x + row * cvec + c) : make_uint4(0, 0, 0, 0);
     }
+    // the row is unpacked to fp32 once and stays in registers for all three passes
+    float xf[VPT][8];
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sum += bf16lo_to_f32(w[j]) + bf16hi_to_f32(w[j]);
+      for (int j = 0; j < 4; ++j) {
+        xf[i][2 * j] = bf16lo_to_f32(w[j]);
+        xf[i][2 * j + 1] = bf16hi_to_f32(w[j]);
+        sum += xf[i][2 * j] + xf[i][2 * j + 1];
+      }
     }
     const float mean = row_allreduce_sum<TPR>(sum, red) * inv_c;
     float sq = 0.f;
@@ -106,10 +112,9 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + i * TPR;
       if (c < cvec) {
-        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a = bf16lo_to_f32(w[j]) - mean, b = bf16hi_to_f32(w[j]) - mean;
+          const float a = xf[i][2 * j] - mean, b = xf[i][2 * j + 1] - mean;
           sq += a * a + b * b;
         }
       }
@@ -122,11 +127,10 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
       if (c < cvec) {
         const uint4 fc = fac_s[c], sh = shf_s[c];
         const uint32_t fcw[4] = {fc.x, fc.y, fc.z, fc.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
-        uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const uint32_t n = pack_bf16x2_rn((bf16lo_to_f32(w[j]) - mean) * rstd,
-                                            (bf16hi_to_f32(w[j]) - mean) * rstd);
+          const uint32_t n = pack_bf16x2_rn((xf[i][2 * j] - mean) * rstd, (xf[i][2 * j + 1] - mean) * rstd);
           // The two modulation roundings as packed bf16 instructions on the FMA pipe.  Each is
           // the correctly rounded product / sum of two bf16 values, which is what the fp32
           // formulation computes too: the fp32 product of two bf16 is exact, and the fp32 sum
@@ -283,12 +287,13 @@ int launch_layernorm_mod(const void* x, const void* scale, const void* shift, vo
           (const uint4*)x, (const uint4*)scale, (const uint4*)shift, (uint4*)out_bf16, nullptr,  \
           nullptr, M, cvec, inv_c, eps);                                                         \
   } while (0)
+  // at most 6 vectors (48 fp32 values) per thread, so the unpacked row fits in registers
   if (C <= 1024) B2_LN(32, 4);
-  else if (C <= 2048) B2_LN(32, 8);
-  else if (C <= 3072) B2_LN(32, 12);
-  else if (C <= 4096) B2_LN(64, 8);
-  else if (C <= 6144) B2_LN(64, 12);
-  else if (C <= 8192) B2_LN(128, 8);
+  else if (C <= 2048) B2_LN(64, 4);
+  else if (C <= 3072) B2_LN(64, 6);
+  else if (C <= 4096) B2_LN(128, 4);
+  else if (C <= 6144) B2_LN(128, 6);
+  else if (C <= 8192) B2_LN(256, 4);
   else return fail(B2_NOT_WHITELISTED, "layernorm_mod: C=%lld exceeds 8192", (long long)C);
 #undef B2_LN
   return check_launch("layernorm_mod");
