@@ -93,6 +93,19 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
       const int c = lane + i * TPR;
       v[i] = (live && c < cvec) ? ldg_stream(x + row * cvec + c) : make_uint4(0, 0, 0, 0);
     }
+    // the row this slot handles next is requested into L2 now: the three dependent reductions
+    // below leave few loads in flight per SM otherwise
+    {
+      const int64_t next = row + (int64_t)gridDim.x * RPC;
+      if (next < M) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {   // one 128-byte line per 8 lanes' vectors
+          const int c = lane + i * TPR;
+          if (c < cvec && (lane & 7) == 0)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(x + next * cvec + c));
+        }
+      }
+    }
     // the row is unpacked to fp32 once and stays in registers for all three passes
     float xf[VPT][8];
     float sum = 0.f;
