@@ -115,17 +115,41 @@ def admit(path: str | os.PathLike | None = None, note: str = "") -> dict:
     digest = sha256_file(p)
     table.setdefault("artifacts", {})[digest] = {"file": p.name, "abi": ABI_VERSION, "note": note}
     table_path.write_text(json.dumps(table, indent=1, sort_keys=True))
+    refresh_audit()
     return table
+
+
+# (audit table path, its mtime in ns, its size, artifact digest) -> the artifact's table entry
+_audit_cache: tuple | None = None
+
+
+def refresh_audit() -> None:
+    """Forget the cached audit entry (the next `audited()` reads the table again)."""
+    global _audit_cache
+    _audit_cache = None
+
+
+def _audit_entry():
+    """The loaded artifact's entry in the audit table, or None.  Gated calls ask this several
+    times per operator call, so the table is parsed once and kept until the file changes
+    (one `stat` per question instead of a read and a JSON parse)."""
+    global _audit_cache
+    digest = loaded_sha256()
+    path = audit_path()
+    st = os.stat(path)
+    key = (str(path), st.st_mtime_ns, st.st_size, digest)
+    if _audit_cache is None or _audit_cache[0] != key:
+        table = json.loads(path.read_text())
+        _audit_cache = (key, table.get("artifacts", {}).get(digest))
+    return _audit_cache[1]
 
 
 def audited(op: str | None = None) -> bool:
     """True iff the loaded artifact's sha256 is in the audit table."""
     try:
-        digest = loaded_sha256()
-        table = json.loads(audit_path().read_text())
+        entry = _audit_entry()
     except (RuntimeError, OSError, json.JSONDecodeError):
         return False
-    entry = table.get("artifacts", {}).get(digest)
     if entry is None:
         return False
     ops = entry.get("ops")

@@ -39,6 +39,39 @@ class SPContext:
         self.local_length = local_length
 
 
+# key of the host's `transformer_options` dict under which the sequence-parallel state
+# travels (an SPContext-like object or a dict with the same four fields)
+SP_OPTIONS_KEY = "sequence_parallel"
+
+
+def context_from_transformer_options(transformer_options):
+    """Default context resolver: what the reference obtains from its host with
+    `attention_context(kwargs["transformer_options"])` (launcher :1167-1173).
+
+    Not a dict -> None (the call is refused with `sp_world`, as in the reference).  A dict
+    without sequence-parallel state describes a single-GPU run: world size 1.  Otherwise the
+    entry under SP_OPTIONS_KEY is used: any object with `world_size` (and optionally `rank`,
+    `sequence_splits`, `local_length`), or a dict with those keys.  A host whose model keeps
+    this state elsewhere registers its own resolver on the Gates object."""
+    if not isinstance(transformer_options, dict):
+        return None
+    state = transformer_options.get(SP_OPTIONS_KEY)
+    if state is None:
+        return SPContext(0, 1)
+    if isinstance(state, dict):
+        return SPContext(state.get("rank", 0), state.get("world_size", 1),
+                         state.get("sequence_splits"), state.get("local_length"))
+    return state if hasattr(state, "world_size") else None
+
+
+def resolve_precision(attn_precision, dtype):
+    """Default precision resolver: the requested precision as given.  A host that can force
+    an fp32 upcast regardless of the argument (the reference calls its host's
+    `get_attn_precision(attn_precision, query.dtype)`, launcher :1165) registers that
+    function on the Gates object, so a forced upcast is refused with `precision`."""
+    return attn_precision
+
+
 def expected_splits(seq: int, world: int) -> tuple[int, ...]:
     base, rem = divmod(seq, world)
     return tuple(base + (1 if r < rem else 0) for r in range(world))
@@ -94,15 +127,24 @@ def flash_gate(g: Gates, query, key, value, heads, mask, skip_reshape, kwargs, s
 
 def attention(query, key, value, heads, mask=None, attn_precision=None, skip_reshape=False,
               skip_output_reshape=False, gates: Gates | None = None, sp_context=None, **kwargs):
-    """Drop-in for the host's `optimized_attention(q, k, v, heads, ...)`."""
+    """Drop-in for the host's `optimized_attention(q, k, v, heads, ...)`.
+
+    The sequence-parallel context comes from `kwargs["transformer_options"]` through the
+    gates' `context_resolver` (what the reference does, launcher :1167-1173) unless the caller
+    passes `sp_context=` explicitly; the precision the gate tests and logs is the one the
+    gates' `precision_resolver` returns for (attn_precision, query.dtype) (launcher :1165)."""
     g = gates if gates is not None else default_gates()
+    if sp_context is None:
+        resolver = getattr(g, "context_resolver", None) or context_from_transformer_options
+        sp_context = resolver(kwargs.get("transformer_options"))
+    precision = (getattr(g, "precision_resolver", None) or resolve_precision)(attn_precision, query.dtype)
     ok, reason, chunked = flash_gate(g, query, key, value, heads, mask, skip_reshape, kwargs,
-                                     sp_context, attn_precision)
+                                     sp_context, precision)
     c = g.counters["flash"]
     if not ok:
         tensors = (query, key, value)
         signature = (tuple(query.shape), tuple(tuple(t.stride()) for t in tensors), heads,
-                     mask is not None, skip_reshape, "scale" in kwargs, str(attn_precision),
+                     mask is not None, skip_reshape, "scale" in kwargs, str(precision),
                      getattr(sp_context, "world_size", None),
                      tuple(t.requires_grad for t in tensors))
         c.fallbacks[reason] += 1

@@ -103,9 +103,12 @@ class DiTBlock:
         else:
             ops.gate_residual_(x, ops.int8_gemm_dequant(q8, s.view(-1), wq, ws, bias), gate)
 
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                taps: dict | None = None) -> torch.Tensor:
         """x bf16 [L, C] (this rank's tokens); cos/sin fp32 [L, 64] for the same rows.
-        Returns a new tensor."""
+        Returns a new tensor.  `taps`, when given, receives intermediate tensors for parity
+        checks: "attn" = the attention output rows [L, H*D] that feed the out-projection and,
+        on the single-GPU path, "qkv" = the normed and rotated projections [L,3,H,D]."""
         p = self.p
         L = x.shape[0]
         x = x.clone()
@@ -117,11 +120,16 @@ class DiTBlock:
             # the out-projection's quantizer reads the reverse all-to-all's buffer in place
             send = ops.qk_norm_rope_pack(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin,
                                          self.sp.world, self.head_chunks)
-            q8, s = ops.quantize_int8_rowwise_gathered(
-                self.sp.attention_packed(send, self._attn, overlap=self.overlap))
+            gathered = self.sp.attention_packed(send, self._attn, overlap=self.overlap)
+            if taps is not None:
+                taps["attn"] = UlyssesSP.unpack_gathered(gathered).contiguous()
+            q8, s = ops.quantize_int8_rowwise_gathered(gathered)
         else:
             ops.qk_norm_rope_(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin)
-            q8, s = ops.quantize_int8_rowwise(self.attention(qkv))
+            attn_rows = self.attention(qkv)
+            if taps is not None:
+                taps["qkv"], taps["attn"] = qkv, attn_rows
+            q8, s = ops.quantize_int8_rowwise(attn_rows)
         self._linear_residual(x, p["gate1"], q8, s, p["wq_out"], p["ws_out"], p["b_out"])
         q8, s = ops.layernorm_mod_quant(x, p["scale2"], p["shift2"])
         f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/b2dit.h"
 
 namespace b2 {
@@ -16,6 +18,39 @@ int fail(int status, const char* fmt, ...);
 int check_launch(const char* what);
 
 constexpr int kNumSMsB200 = 148;
+
+// One-time launch set-up that CUDA keeps PER DEVICE (cudaFuncSetAttribute, occupancy
+// queries, the SM count): a process that drives several GPUs must repeat it on each, and
+// two threads may make the first call at once.  get() runs `setup(device, slot)` once for
+// the CURRENT device under a lock and afterwards hands back that device's slot.
+struct DeviceSlot {
+  bool ready = false;
+  int a = 0, b = 0;   // kernel-specific values (e.g. enabled flag, cluster count, SM count)
+};
+class PerDeviceSetup {
+ public:
+  template <class Setup>
+  int get(const char* what, Setup&& setup, const DeviceSlot** out) {
+    int dev = -1;
+    const cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "%s: cudaGetDevice: %s", what, cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(B2_TOO_LARGE, "%s: device index %d not supported", what, dev);
+    std::lock_guard<std::mutex> lock(mutex_);
+    DeviceSlot& slot = slots_[dev];
+    if (!slot.ready) {
+      const int st = setup(dev, slot);
+      if (st != B2_OK) return st;
+      slot.ready = true;
+    }
+    *out = &slot;
+    return B2_OK;
+  }
+
+ private:
+  static constexpr int kMaxDevices = 64;
+  std::mutex mutex_;
+  DeviceSlot slots_[kMaxDevices];
+};
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

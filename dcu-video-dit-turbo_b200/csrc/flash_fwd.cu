@@ -508,8 +508,9 @@ int launch_bounded_wait_selftest(cudaStream_t stream) {
 int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
                      cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceSetup per_device;
+  const DeviceSlot* slot = nullptr;
+  const int setup_status = per_device.get("flash_fwd", [](int, DeviceSlot&) -> int {
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_TOTAL);
     if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "flash_fwd: smem attribute: %s", cudaGetErrorString(e));
@@ -519,8 +520,9 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int
     if (4 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE > 5 * ((fa.numRegs + 7) / 8 * 8))
       return fail(B2_LAUNCH_FAILED, "flash_fwd: register split %d/%d does not fit %d launch registers",
                   B2_FLASH_REGS_SOFTMAX, B2_FLASH_REGS_SERVICE, fa.numRegs);
-    attr_set = true;
-  }
+    return B2_OK;
+  }, &slot);
+  if (setup_status != B2_OK) return setup_status;
   if (H > 65535 || B > 65535) return fail(B2_TOO_LARGE, "flash_fwd: heads/batch exceed the launch grid");
   CUtensorMap tq, tk, tv;
   FlashArgs a;

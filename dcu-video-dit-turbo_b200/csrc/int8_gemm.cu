@@ -255,13 +255,17 @@ int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* o
   // large M: two CTAs per 256x256 tile (less operand traffic per SM); else one CTA per tile
   const int pair_status = launch_int8_gemm_pair(A, W, out_i32, out_bf16, rs, cs, bias, bias_kind, gate, residual, M, N, K, stream);
   if (pair_status >= 0) return pair_status;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceSetup per_device;
+  const DeviceSlot* slot = nullptr;
+  const int setup_status = per_device.get("int8_gemm", [](int dev, DeviceSlot& s) -> int {
     cudaError_t e = cudaFuncSetAttribute(int8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_TOTAL);
     if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "int8_gemm: smem attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+    s.a = kNumSMsB200;
+    cudaDeviceGetAttribute(&s.a, cudaDevAttrMultiProcessorCount, dev);
+    return B2_OK;
+  }, &slot);
+  if (setup_status != B2_OK) return setup_status;
   CUtensorMap ta, tb;
   int st = encode_k_major_map(&ta, A, M, K, BM);
   if (st != B2_OK) return st;
@@ -289,9 +293,7 @@ int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* o
   a.epi.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
   a.epi.residual = reinterpret_cast<__nv_bfloat16*>(residual);
 
-  int dev = 0, sms = kNumSMsB200;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = slot->a;
   const int grid = a.num_tiles < sms ? a.num_tiles : sms;
   int8_gemm_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, a);
   return check_launch("int8_gemm");

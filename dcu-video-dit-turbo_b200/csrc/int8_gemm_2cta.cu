@@ -299,20 +299,19 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
                           const float* rs, const float* cs, const void* bias, int bias_kind,
                           const void* gate, void* residual, int64_t M, int64_t N, int64_t K,
                           cudaStream_t stream) {
-  static int enabled = -1, max_clusters = 0;
-  if (enabled < 0) {
+  // slot.a = 1 when the pair kernel can run on this device, slot.b = resident clusters
+  static PerDeviceSetup per_device;
+  const DeviceSlot* slot = nullptr;
+  const int setup_status = per_device.get("int8_gemm (CTA pair)", [](int dev, DeviceSlot& s) -> int {
     const char* env = getenv("B2_GEMM_PAIR");
-    enabled = (env && env[0] == '0') ? 0 : 1;
-    if (enabled) {
-      if (cudaFuncSetAttribute(int8_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               SMEM_TOTAL) != cudaSuccess) {
-        cudaGetLastError();
-        enabled = 0;
-      }
+    s.a = (env && env[0] == '0') ? 0 : 1;
+    if (s.a && cudaFuncSetAttribute(int8_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_TOTAL) != cudaSuccess) {
+      cudaGetLastError();
+      s.a = 0;
     }
-    if (enabled) {
-      int dev = 0, sms = kNumSMsB200;
-      cudaGetDevice(&dev);
+    if (s.a) {
+      int sms = kNumSMsB200;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
@@ -328,12 +327,15 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
       int n = 0;
       if (cudaOccupancyMaxActiveClusters(&n, int8_gemm_2cta_kernel, &cfg) != cudaSuccess || n < 1) {
         cudaGetLastError();
-        enabled = 0;
+        s.a = 0;
       } else {
-        max_clusters = n;
+        s.b = n;
       }
     }
-  }
+    return B2_OK;
+  }, &slot);
+  if (setup_status != B2_OK) return setup_status;
+  const int enabled = slot->a, max_clusters = slot->b;
   if (!enabled || M < 2 * BM) return -1;
 
   CUtensorMap ta, tb;

@@ -131,10 +131,15 @@ class Gates:
         self.fallbacks: dict[str, Callable] = {}
         self.counters = {n: GateCounters(n) for n in
                          ("exact_quantizer", "vec4_epilogue", "epilogue", "unpadded_gemm",
-                          "fused_gemm", "mod_scale_shift", "swiglu_quant", "flash")}
+                          "fused_gemm", "mod_scale_shift", "swiglu_quant", "flash", "convrot")}
         self.flash_fallback_signatures: set = set()
         self.flash_head_chunk_calls = 0
         self._flash_first_call = True
+        # host hooks of the attention gate (None = the defaults in attention.py):
+        # context_resolver(transformer_options) -> sequence-parallel context or None,
+        # precision_resolver(attn_precision, dtype) -> the precision the host will really use
+        self.context_resolver: Callable | None = None
+        self.precision_resolver: Callable | None = None
         # start-up invariants (launcher :936-941): vec4 needs the scalar epilogue as
         # its fallback; any enabled feature needs a loadable artifact NOW.
         if self.vec4_epilogue_enabled and not self.epilogue_enabled:
@@ -171,7 +176,7 @@ class Gates:
 
     def register_fallbacks(self, **fns: Callable) -> None:
         """Host-supplied original implementations: quantize, swiglu_quantize, int_mm,
-        epilogue, mod_scale_shift, attention."""
+        epilogue, mod_scale_shift, attention, input_act, convrot_rotate."""
         self.fallbacks.update(fns)
 
     def _fallback(self, name: str) -> Callable:
@@ -302,6 +307,15 @@ class Gates:
             return False, "dtype"
         if x_8.dim() != 2 or weight_t.dim() != 2 or x_8.shape[1] != weight_t.shape[0]:
             return False, "shape"
+        # everything the kernel wrapper would reject is a counted refusal here, so such a
+        # call reaches the host's GEMM (which accepts any layout) instead of raising
+        if x_8.device != weight_t.device:
+            return False, "device_mismatch"
+        if not x_8.is_contiguous():
+            return False, "noncontiguous"
+        stride = weight_t.stride()
+        if stride is not None and tuple(stride) != (1, weight_t.shape[0]):
+            return False, "weight_layout"    # not the transpose view of a contiguous [N,K] weight
         if (x_8.shape[0], x_8.shape[1], weight_t.shape[1]) not in GEMM_SHAPES:
             return False, "MKN"
         if not self.is_arch(x_8):
@@ -325,11 +339,19 @@ class Gates:
             return False, "bias_dtype"
         if not (x_8.is_cuda and weight.is_cuda and row_scale.is_cuda and col_scale.is_cuda):
             return False, "device"
+        if not (x_8.device == weight.device == row_scale.device == col_scale.device):
+            return False, "device_mismatch"
+        if bias is not None and not (bias.is_cuda and bias.device == x_8.device):
+            return False, "bias_device"
         if not (x_8.is_contiguous() and weight.is_contiguous() and row_scale.is_contiguous()
                 and col_scale.is_contiguous()):
             return False, "noncontiguous"
+        if bias is not None and not bias.is_contiguous():
+            return False, "bias_noncontiguous"
         if x_8.dim() != 2 or weight.dim() != 2 or x_8.shape[1] != weight.shape[1]:
             return False, "shape"
+        if bias is not None and bias.numel() not in (0, weight.shape[0]):
+            return False, "bias_shape"
         if (x_8.shape[0], x_8.shape[1], weight.shape[0]) not in GEMM_SHAPES:
             return False, "MKN"
         if row_scale.numel() != x_8.shape[0] or col_scale.numel() != weight.shape[0]:

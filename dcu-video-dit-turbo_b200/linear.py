@@ -10,8 +10,12 @@ reference's three-kernel route, each behind its own gate:
     reference points at, :976);
   * GEMM + epilogue -> the single tcgen05 kernel with the epilogue fused, which
     skips the int32 [M,N] round trip.
-ConvRot is not implemented (the reference's whitelisted DiT linears do not use
-it): `convrot=True` raises.
+ConvRot (launcher :993-999) has no kernel here: its Hadamard helpers belong to the host's
+quantization package, which is not part of the reference tree, so the rotation cannot be
+pinned.  `convrot=True` is therefore a counted refusal (reason `convrot`): the rotation of
+the activation goes to the host's own helper, registered as the `convrot_rotate` fallback
+`(x, groupsize) -> x`, and the rotated activation continues through the gated path below.
+Without a registered helper the call raises, like every refusal without a fallback.
 """
 from __future__ import annotations
 
@@ -26,8 +30,10 @@ def int8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tenso
                 convrot: bool = False, convrot_groupsize: int = 256,
                 input_act: str | None = None, gates: Gates | None = None) -> torch.Tensor:
     g = gates if gates is not None else default_gates()
-    if convrot:
-        raise NotImplementedError("ConvRot is outside the B200 hot path")
+    if convrot and input_act is not None:
+        # the reference applies the input activation first and rotates its result
+        x = g._fallback("input_act")(x, input_act)
+        input_act = None
     k_in = x.shape[-1] // 2 if input_act == "swiglu" else x.shape[-1]
     if k_in != weight.shape[-1]:
         raise ValueError(
@@ -40,6 +46,13 @@ def int8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tenso
         raise ValueError(
             f"INT8 weight scale must be scalar or per-output-channel, got "
             f"{tuple(weight_scale.shape)} for weight shape {tuple(weight.shape)}")
+
+    if convrot:
+        if x.shape[-1] % convrot_groupsize != 0:
+            raise ValueError(
+                f"ConvRot group size {convrot_groupsize} does not divide input features {x.shape[-1]}")
+        g.counters["convrot"].refuse("convrot", x.shape, groupsize=convrot_groupsize)
+        x = g._fallback("convrot_rotate")(x, convrot_groupsize)
 
     orig_shape = x.shape
     x_2d = x.reshape(-1, x.shape[-1])

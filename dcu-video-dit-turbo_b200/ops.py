@@ -42,16 +42,71 @@ def _require(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
-def _call(name: str, t: torch.Tensor, *args, launches: int = 1) -> None:
+class LaunchTimer:
+    """CUDA events around every C-ABI launch made while the context is active.
+
+        with ops.LaunchTimer() as timer:
+            block.forward(x, cos, sin)
+        for rec in timer.results(): ...   # {"name", "ms", "bound", "work"}
+
+    `bound` names the roofline that limits the kernel ("hbm", "int8" or "bf16") and `work`
+    its algorithmic bytes (hbm) or operations per launch, so a caller can turn `ms` into
+    GB/s or TOP/s.  Events are recorded on PyTorch's current stream of the tensor's device
+    (the stream the kernel is enqueued on); nothing synchronises until `results()`."""
+
+    def __init__(self):
+        self._records = []
+
+    def __enter__(self):
+        global _timer
+        self._previous, _timer = _timer, self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = self._previous
+        return False
+
+    def results(self) -> list[dict]:
+        out = []
+        for name, e0, e1, work in self._records:
+            e1.synchronize()
+            bound, amount = work if work is not None else (None, None)
+            out.append({"name": name, "ms": e0.elapsed_time(e1), "bound": bound, "work": amount})
+        return out
+
+
+_timer: LaunchTimer | None = None
+
+
+def _call(name: str, t: torch.Tensor, *args, launches: int = 1, work=None) -> None:
     global launch_count
     lib = _lib.load()
+    timer = _timer
+    if timer is not None:
+        stream = torch.cuda.current_stream(t.device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
     if t.device.index != torch.cuda.current_device():
         with torch.cuda.device(t.device):
             st = getattr(lib, name)(*args)
     else:
         st = getattr(lib, name)(*args)
     _lib.check(st, name)
+    if timer is not None:
+        e1.record(stream)
+        timer._records.append((name, e0, e1, work))
     launch_count += launches
+
+
+def _require_vector(v: torch.Tensor, like: torch.Tensor, numel: int, dtype, what: str) -> None:
+    """A per-column operand handed to the C ABI as a raw pointer: right dtype, on the same
+    CUDA device as the data, contiguous, with exactly `numel` elements."""
+    _require(torch.is_tensor(v) and v.is_cuda and v.device == like.device,
+             f"{what} must be on the same CUDA device as the data")
+    _require(v.dtype == dtype, f"{what} must be {str(dtype).replace('torch.', '')}")
+    _require(v.is_contiguous(), f"{what} must be contiguous")
+    _require(v.numel() == numel, f"{what} must contain exactly {numel} values")
 
 
 def quantize_int8_rowwise(x: torch.Tensor):
@@ -65,7 +120,8 @@ def quantize_int8_rowwise(x: torch.Tensor):
     s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
     if m == 0:
         return [q, s]
-    _call("b2_quantize_int8_rowwise", x, _ptr(x), _ptr(q), s.data_ptr(), m, k, _stream(x))
+    _call("b2_quantize_int8_rowwise", x, _ptr(x), _ptr(q), s.data_ptr(), m, k, _stream(x),
+          work=("hbm", 3 * m * k + 4 * m))
     return [q, s]
 
 
@@ -82,7 +138,7 @@ def swiglu_quantize_int8_rowwise(x: torch.Tensor):
     if m == 0 or k == 0:
         return [q, s]
     _call("b2_swiglu_quantize_int8_rowwise", x, x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k,
-          _stream(x))
+          _stream(x), work=("hbm", 5 * m * k + 4 * m))
     return [q, s]
 
 
@@ -123,7 +179,8 @@ def epilogue(acc: torch.Tensor, row_scale: torch.Tensor, col_scale: torch.Tensor
     if acc.numel() == 0:
         return out
     _call("b2_epilogue", acc, acc.data_ptr(), row_scale.data_ptr(), col_scale.data_ptr(),
-          _ptr(bias) if kind else None, kind, out.data_ptr(), m, n, _stream(acc))
+          _ptr(bias) if kind else None, kind, out.data_ptr(), m, n, _stream(acc),
+          work=("hbm", 6 * m * n + 4 * m + 4 * n + (0, 2, 4)[kind] * n))
     return out
 
 
@@ -141,13 +198,15 @@ def epilogue_vec4(acc: torch.Tensor, row: torch.Tensor, col: torch.Tensor) -> to
     if acc.numel() == 0:
         return out
     _call("b2_epilogue_vec4", acc, acc.data_ptr(), row.data_ptr(), col.data_ptr(), out.data_ptr(),
-          m, n, _stream(acc))
+          m, n, _stream(acc), work=("hbm", 6 * m * n + 4 * m + 4 * n))
     return out
 
 
 def mod_scale_shift_(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
     """In place x = bf16(bf16(x*bf16(1+scale)) + shift); returns x."""
     _require(x.is_cuda and scale.is_cuda and shift.is_cuda, "CUDA tensors required")
+    _require(scale.device == x.device and shift.device == x.device,
+             "all inputs must be on the same device")
     _require(x.is_contiguous() and scale.is_contiguous() and shift.is_contiguous(),
              "contiguous tensors required")
     _require(x.dtype == torch.bfloat16 and scale.dtype == torch.bfloat16
@@ -157,7 +216,7 @@ def mod_scale_shift_(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor) 
     if x.numel() == 0:
         return x
     _call("b2_mod_scale_shift", x, x.data_ptr(), scale.data_ptr(), shift.data_ptr(), x.shape[0],
-          x.shape[1], _stream(x))
+          x.shape[1], _stream(x), work=("hbm", 4 * x.numel() + 4 * x.shape[1]))
     return x
 
 
@@ -165,6 +224,7 @@ def int_mm(a: torch.Tensor, w_t: torch.Tensor) -> torch.Tensor:
     """int32 [M,N] = a[M,K] @ w_t[K,N], with w_t the transpose VIEW of a contiguous
     int8 [N,K] weight: the same operands `torch._int_mm(x_8, weight.T)` receives."""
     _require(a.is_cuda and w_t.is_cuda, "CUDA tensors required")
+    _require(a.device == w_t.device, "all inputs must be on the same device")
     _require(a.dtype == torch.int8 and w_t.dtype == torch.int8, "int8 operands required")
     _require(a.dim() == 2 and w_t.dim() == 2 and a.shape[1] == w_t.shape[0], "shape mismatch")
     _require(a.is_contiguous(), "a must be contiguous")
@@ -175,7 +235,8 @@ def int_mm(a: torch.Tensor, w_t: torch.Tensor) -> torch.Tensor:
     out = torch.empty((m, n), dtype=torch.int32, device=a.device)
     if m == 0 or n == 0:
         return out
-    _call("b2_int8_gemm", a, a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, _stream(a))
+    _call("b2_int8_gemm", a, a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, _stream(a),
+          work=("int8", 2 * m * n * k))
     return out
 
 
@@ -184,6 +245,8 @@ def int8_gemm_dequant(a: torch.Tensor, row_scale: torch.Tensor, w: torch.Tensor,
     """GEMM with the dequant epilogue fused: a int8 [M,K], w int8 [N,K] -> bf16 [M,N]."""
     _require(a.is_cuda and w.is_cuda and row_scale.is_cuda and col_scale.is_cuda,
              "CUDA tensors required")
+    _require(w.device == a.device and row_scale.device == a.device and col_scale.device == a.device,
+             "all inputs must be on the same device")
     _require(a.dtype == torch.int8 and w.dtype == torch.int8, "int8 operands required")
     _require(row_scale.dtype == torch.float32 and col_scale.dtype == torch.float32,
              "scales must be float32")
@@ -199,7 +262,7 @@ def int8_gemm_dequant(a: torch.Tensor, row_scale: torch.Tensor, w: torch.Tensor,
         return out
     _call("b2_int8_gemm_dequant", a, a.data_ptr(), row_scale.data_ptr(), w.data_ptr(),
           col_scale.data_ptr(), _ptr(bias) if kind else None, kind, out.data_ptr(), m, n, k,
-          _stream(a))
+          _stream(a), work=("int8", 2 * m * n * k))
     return out
 
 
@@ -215,8 +278,11 @@ def int8_gemm_dequant_residual_(x: torch.Tensor, gate: torch.Tensor, a: torch.Te
     n = w.shape[0]
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(x.shape) == (m, n),
              "x must be a contiguous CUDA bf16 [M,N] tensor")
-    _require(gate.dtype == torch.bfloat16 and gate.numel() == n and gate.is_contiguous(),
-             "gate must be contiguous bf16 [N]")
+    _require_vector(gate, a, n, torch.bfloat16, "gate")
+    _require(w.is_cuda and w.device == a.device and x.device == a.device
+             and row_scale.is_cuda and row_scale.device == a.device
+             and col_scale.is_cuda and col_scale.device == a.device,
+             "all inputs must be on the same device")
     _require(row_scale.dtype == torch.float32 and col_scale.dtype == torch.float32
              and row_scale.numel() == m and col_scale.numel() == n
              and row_scale.is_contiguous() and col_scale.is_contiguous(), "scale mismatch")
@@ -224,7 +290,7 @@ def int8_gemm_dequant_residual_(x: torch.Tensor, gate: torch.Tensor, a: torch.Te
     if m and n:
         _call("b2_int8_gemm_dequant_residual", a, a.data_ptr(), row_scale.data_ptr(), w.data_ptr(),
               col_scale.data_ptr(), _ptr(bias) if kind else None, kind, gate.data_ptr(),
-              x.data_ptr(), m, n, k, _stream(a))
+              x.data_ptr(), m, n, k, _stream(a), work=("int8", 2 * m * n * k))
     return x
 
 
@@ -239,6 +305,9 @@ def int8_linear(x: torch.Tensor, w: torch.Tensor, col_scale: torch.Tensor,
              "w must be a contiguous CUDA int8 [N,K] tensor")
     act = {None: ACT_NONE, "swiglu": ACT_SWIGLU}.get(input_act, -1)
     _require(act >= 0, f"unknown input activation {input_act!r}")
+    _require(act != ACT_SWIGLU or x.shape[1] % 2 == 0, "swiglu input width must be even")
+    _require(w.device == x.device and col_scale.is_cuda and col_scale.device == x.device,
+             "all inputs must be on the same device")
     m = x.shape[0]
     k = x.shape[1] // 2 if act == ACT_SWIGLU else x.shape[1]
     n = w.shape[0]
@@ -259,7 +328,7 @@ def int8_linear(x: torch.Tensor, w: torch.Tensor, col_scale: torch.Tensor,
         _require(qs.numel() >= m * k and ss.numel() >= m, "scratch too small")
     _call("b2_int8_linear", x, x.data_ptr(), act, w.data_ptr(), col_scale.data_ptr(),
           _ptr(bias) if kind else None, kind, out.data_ptr(), qs.data_ptr(), ss.data_ptr(), m, n,
-          k, _stream(x), launches=2)
+          k, _stream(x), launches=2, work=("int8", 2 * m * n * k))
     return out
 
 
@@ -290,7 +359,7 @@ def fwd_bhsd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: f
     for t in (q, k, v):
         strides += [t.stride(0) if b > 1 else 0, t.stride(1) if h > 1 else 0, t.stride(2)]
     _call("b2_flash_fwd", q, q.data_ptr(), k.data_ptr(), v.data_ptr(), storage.data_ptr(), b, h, s,
-          *strides, scale, _stream(q))
+          *strides, scale, _stream(q), work=("bf16", 4 * b * h * s * s * d))
     return out
 
 
@@ -301,11 +370,12 @@ def layernorm_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor,
     """bf16 [M,C]: LayerNorm without affine, then the mod-scale-shift contract."""
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous(),
              "x must be a contiguous CUDA bf16 [M,C] tensor")
-    _require(scale.numel() == x.shape[1] and shift.numel() == x.shape[1], "shape mismatch")
+    _require_vector(scale, x, x.shape[1], torch.bfloat16, "scale")
+    _require_vector(shift, x, x.shape[1], torch.bfloat16, "shift")
     out = torch.empty_like(x)
     if x.numel():
         _call("b2_layernorm_mod", x, x.data_ptr(), scale.data_ptr(), shift.data_ptr(),
-              out.data_ptr(), x.shape[0], x.shape[1], eps, _stream(x))
+              out.data_ptr(), x.shape[0], x.shape[1], eps, _stream(x), work=("hbm", 4 * x.numel()))
     return out
 
 
@@ -314,13 +384,14 @@ def layernorm_mod_quant(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tenso
     """LayerNorm + modulation + rowwise quantizer in one pass: [int8 [M,C], fp32 [M,1]]."""
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous(),
              "x must be a contiguous CUDA bf16 [M,C] tensor")
-    _require(scale.numel() == x.shape[1] and shift.numel() == x.shape[1], "shape mismatch")
+    _require_vector(scale, x, x.shape[1], torch.bfloat16, "scale")
+    _require_vector(shift, x, x.shape[1], torch.bfloat16, "shift")
     m, c = x.shape
     q = torch.empty((m, c), dtype=torch.int8, device=x.device)
     s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
     if x.numel():
         _call("b2_layernorm_mod_quant", x, x.data_ptr(), scale.data_ptr(), shift.data_ptr(),
-              q.data_ptr(), s.data_ptr(), m, c, eps, _stream(x))
+              q.data_ptr(), s.data_ptr(), m, c, eps, _stream(x), work=("hbm", 3 * m * c + 4 * m))
     return [q, s]
 
 
@@ -331,15 +402,15 @@ def qk_norm_rope_(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Ten
              and qkv.is_contiguous() and qkv.shape[1] == 3 and qkv.shape[3] == 128,
              "qkv must be a contiguous CUDA bf16 [S,3,H,128] tensor")
     s, _, h, _ = qkv.shape
-    _require(cos.dtype == torch.float32 and sin.dtype == torch.float32
-             and tuple(cos.shape) == (s, 64) and tuple(sin.shape) == (s, 64)
-             and cos.is_contiguous() and sin.is_contiguous(), "cos/sin must be fp32 [S,64]")
-    _require(q_weight.numel() == 128 and k_weight.numel() == 128
-             and q_weight.dtype == torch.bfloat16 and k_weight.dtype == torch.bfloat16,
-             "norm weights must be bf16 [128]")
+    _require(tuple(cos.shape) == (s, 64) and tuple(sin.shape) == (s, 64), "cos/sin must be fp32 [S,64]")
+    _require_vector(cos, qkv, s * 64, torch.float32, "cos")
+    _require_vector(sin, qkv, s * 64, torch.float32, "sin")
+    _require_vector(q_weight, qkv, 128, torch.bfloat16, "q norm weight")
+    _require_vector(k_weight, qkv, 128, torch.bfloat16, "k norm weight")
     if s:
         _call("b2_qk_norm_rope", qkv, qkv.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(),
-              cos.data_ptr(), sin.data_ptr(), s, h, eps, _stream(qkv))
+              cos.data_ptr(), sin.data_ptr(), s, h, eps, _stream(qkv),
+              work=("hbm", 8 * s * h * 128 + 512 * s))
     return qkv
 
 
@@ -355,18 +426,17 @@ def qk_norm_rope_pack(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch
     L, _, h, _ = qkv.shape
     _require(world > 0 and chunks > 0 and h % (world * chunks) == 0,
              "world*chunks must divide the head count")
-    _require(cos.dtype == torch.float32 and sin.dtype == torch.float32
-             and tuple(cos.shape) == (L, 64) and tuple(sin.shape) == (L, 64)
-             and cos.is_contiguous() and sin.is_contiguous(), "cos/sin must be fp32 [L,64]")
-    _require(q_weight.numel() == 128 and k_weight.numel() == 128
-             and q_weight.dtype == torch.bfloat16 and k_weight.dtype == torch.bfloat16,
-             "norm weights must be bf16 [128]")
+    _require(tuple(cos.shape) == (L, 64) and tuple(sin.shape) == (L, 64), "cos/sin must be fp32 [L,64]")
+    _require_vector(cos, qkv, L * 64, torch.float32, "cos")
+    _require_vector(sin, qkv, L * 64, torch.float32, "sin")
+    _require_vector(q_weight, qkv, 128, torch.bfloat16, "q norm weight")
+    _require_vector(k_weight, qkv, 128, torch.bfloat16, "k norm weight")
     c = h // (world * chunks)
     send = torch.empty((chunks, world, L, c, 3, 128), dtype=torch.bfloat16, device=qkv.device)
     if L:
         _call("b2_qk_norm_rope_pack", qkv, qkv.data_ptr(), send.data_ptr(), q_weight.data_ptr(),
               k_weight.data_ptr(), cos.data_ptr(), sin.data_ptr(), L, h, world, chunks, eps,
-              _stream(qkv))
+              _stream(qkv), work=("hbm", 12 * L * h * 128 + 512 * L))
     return send
 
 
@@ -386,7 +456,7 @@ def quantize_int8_rowwise_gathered(x: torch.Tensor):
     s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
     if m:
         _call("b2_quantize_int8_rowwise_gathered", x, x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k,
-              world, chunks, _stream(x))
+              world, chunks, _stream(x), work=("hbm", 3 * m * k + 4 * m))
     return [q, s]
 
 
@@ -402,24 +472,28 @@ def images_to_u8(images: torch.Tensor) -> torch.Tensor:
     out = torch.empty(images.shape, dtype=torch.uint8, device=images.device)
     if images.numel():
         _call("b2_images_to_u8", images, images.data_ptr(), _FRAME_DTYPES[images.dtype], out.data_ptr(),
-              images.numel(), _stream(images))
+              images.numel(), _stream(images),
+              work=("hbm", images.numel() * (images.element_size() + 1)))
     return out
 
 
 def gate_residual_(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     """In place x = bf16(x + bf16(gate*y)); returns x."""
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
-             and y.is_contiguous() and y.shape == x.shape and y.dtype == torch.bfloat16
-             and gate.numel() == x.shape[1] and gate.dtype == torch.bfloat16,
-             "x,y must be contiguous CUDA bf16 [M,C]; gate bf16 [C]")
+             and y.is_cuda and y.device == x.device and y.is_contiguous() and y.shape == x.shape
+             and y.dtype == torch.bfloat16,
+             "x,y must be contiguous bf16 [M,C] tensors on the same CUDA device")
+    _require_vector(gate, x, x.shape[1], torch.bfloat16, "gate")
     if x.numel():
         _call("b2_gate_residual", x, x.data_ptr(), y.data_ptr(), gate.data_ptr(), x.shape[0],
-              x.shape[1], _stream(x))
+              x.shape[1], _stream(x), work=("hbm", 6 * x.numel()))
     return x
 
 
 def check_device_status(device=None) -> None:
-    """Synchronise and raise if a bounded device-side wait gave up."""
+    """Synchronise and raise if a bounded device-side wait gave up (on `device`, default:
+    the current device; the status word lives in each device's copy of the library image)."""
     lib = _lib.load()
-    stream = torch.cuda.current_stream(device).cuda_stream
-    _lib.check(lib.b2_check_device_status(stream), "b2_check_device_status")
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.b2_check_device_status(stream), "b2_check_device_status")

@@ -135,7 +135,9 @@ int b2_int8_linear(const void* x_bf16, int input_act, const int8_t* W, const flo
  * otherwise B2_TOO_LARGE.  All calls on a GPU share that array and it keeps the previous
  * call's contents (nothing in it needs to start at zero): calls that can overlap on the GPU
  * race, so serialise them.  The first call on each device resolves the array's address;
- * make it during start-up, before any stream capture.  Allocates nothing.
+ * make it during start-up, before any stream capture.  The array that is used belongs to
+ * the CURRENT device (cudaGetDevice) at the time of the call: make the device that owns x,
+ * W and out current first, as for every other entry point.  Allocates nothing.
  * This entry point has no counterpart in the reference project. */
 int b2_int8_linear_noalloc(const void* x_bf16, int input_act, const int8_t* W,
                            const float* col_scale, const void* bias, int bias_kind, void* out_bf16,

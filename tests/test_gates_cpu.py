@@ -195,6 +195,126 @@ def test_flash_gate(pkg, gates):
     assert A.flash_gate(gates, q, k, v, H, None, True, {}, sp1)[1] == "disabled"
 
 
+def test_attention_wired_as_the_host_calls_it(pkg, gates, monkeypatch):
+    """The launcher swap `optimized_attention = lambda *a, **k: attention(*a, gates=g, **k)`:
+    the host passes `transformer_options`, never `sp_context`.  A single-GPU host (no
+    sequence-parallel state in the options) and a sequence-parallel host must both reach the
+    kernel; a host without options, or one whose resolved precision is fp32 although the
+    argument is None, must reach the registered original attention."""
+    A = pkg.attention
+    S, H = 23638, 24
+    launched, fell_back = [], []
+    monkeypatch.setattr(A.ops, "fwd_bhsd", lambda q, k, v, scale: launched.append(scale) or "flash")
+    monkeypatch.setattr(A.ops, "check_device_status", lambda device=None: None)
+    monkeypatch.setattr(A.torch.cuda, "synchronize", lambda device=None: None)
+    gates.register_fallbacks(attention=lambda q, k, v, heads, **kw: fell_back.append(sorted(kw)) or "host")
+    host_attention = lambda *a, **k: A.attention(*a, gates=gates, **k)      # INTEGRATION.md wiring
+    q, k, v = (FakeTensor((1, H, S, 128), torch.bfloat16, stride=(S * H * 128, 128, H * 128, 1))
+               for _ in range(3))
+    out = host_attention(q, k, v, H, skip_reshape=True, skip_output_reshape=True, transformer_options={})
+    assert out == "flash" and len(launched) == 1 and gates.counters["flash"].hits == 1
+    # sequence-parallel state travels inside transformer_options
+    splits = A.expected_splits(109099, 8)
+    qc, kc, vc = (FakeTensor((1, 3, 109099, 128), torch.bfloat16, stride=(0, 384, 3 * 384, 1)) for _ in range(3))
+    opts = {A.SP_OPTIONS_KEY: {"rank": 3, "world_size": 8, "sequence_splits": splits, "local_length": 13637}}
+    assert host_attention(qc, kc, vc, 3, skip_reshape=True, skip_output_reshape=True,
+                          transformer_options=opts) == "flash"
+    assert gates.flash_head_chunk_calls == 1
+    opts_obj = {A.SP_OPTIONS_KEY: A.SPContext(3, 8, splits, 13637)}
+    assert host_attention(qc, kc, vc, 3, skip_reshape=True, skip_output_reshape=True,
+                          transformer_options=opts_obj) == "flash"
+    # no options at all: refused like the reference (sp_world), original arguments forwarded
+    assert host_attention(q, k, v, H, skip_reshape=True) == "host"
+    assert gates.counters["flash"].fallbacks["sp_world"] == 1
+    assert "attn_precision" in fell_back[-1] and "skip_output_reshape" in fell_back[-1]
+    # host-resolved precision: a forced fp32 upcast with attn_precision=None is refused
+    gates.precision_resolver = lambda attn_precision, dtype: torch.float32
+    assert host_attention(q, k, v, H, skip_reshape=True, transformer_options={}) == "host"
+    assert gates.counters["flash"].fallbacks["precision"] == 1
+    gates.precision_resolver = None
+    # a host with its own place for the state registers a resolver
+    gates.context_resolver = lambda options: A.SPContext(0, 2, A.expected_splits(S, 2), 11819)
+    assert host_attention(q, k, v, H, skip_reshape=True, skip_output_reshape=True) == "flash"
+    assert len(launched) == 4
+
+
+def test_every_input_the_wrappers_reject_is_a_counted_refusal(gates):
+    """Reasons in front of MKN / arch for the two GEMM gates: layouts and devices that
+    ops.int_mm / ops.int8_gemm_dequant would raise on go to the fallback instead."""
+    a8 = FakeTensor((23638, 3072), torch.int8, stride=(3072, 1))
+    w8t = FakeTensor((3072, 9216), torch.int8, stride=(1, 3072))
+    assert gates.unpadded_gemm_gate(a8, w8t) == (True, "eligible")
+    assert gates.unpadded_gemm_gate(a8, FakeTensor((3072, 9216), torch.int8, stride=(9216, 1)))[1] == "weight_layout"
+    assert gates.unpadded_gemm_gate(FakeTensor((23638, 3072), torch.int8, contiguous=False), w8t)[1] == "noncontiguous"
+    assert gates.unpadded_gemm_gate(a8, FakeTensor((3072, 9216), torch.int8, device="cuda:1"))[1] == "device_mismatch"
+    rs, cs = FakeTensor((23638,), torch.float32), FakeTensor((9216,), torch.float32)
+    w8 = FakeTensor((9216, 3072), torch.int8)
+    ok_bias = FakeTensor((9216,), torch.bfloat16)
+    assert gates.fused_gemm_gate(a8, rs, w8, cs, ok_bias, torch.bfloat16) == (True, "eligible")
+    assert gates.fused_gemm_gate(a8, rs, FakeTensor((9216, 3072), torch.int8, device="cuda:1"), cs, None,
+                                 torch.bfloat16)[1] == "device_mismatch"
+    assert gates.fused_gemm_gate(a8, rs, w8, cs, FakeTensor((9216,), torch.bfloat16, device="cuda:1"),
+                                 torch.bfloat16)[1] == "bias_device"
+    assert gates.fused_gemm_gate(a8, rs, w8, cs, FakeTensor((9216,), torch.bfloat16, is_cuda=False),
+                                 torch.bfloat16)[1] == "bias_device"
+    assert gates.fused_gemm_gate(a8, rs, w8, cs, FakeTensor((9216,), torch.bfloat16, contiguous=False),
+                                 torch.bfloat16)[1] == "bias_noncontiguous"
+    assert gates.fused_gemm_gate(a8, rs, w8, cs, FakeTensor((9215,), torch.bfloat16), torch.bfloat16)[1] == "bias_shape"
+    # the refusal is counted and served by the host's GEMM
+    gates.register_fallbacks(int_mm=lambda a, wt: "host_gemm")
+    assert gates.int8_matmul(a8, FakeTensor((3072, 9216), torch.int8, stride=(9216, 1))) == "host_gemm"
+    assert gates.dump_counters()["unpadded_gemm"]["reasons"] == {"weight_layout": 1}
+
+
+def test_convrot_is_a_counted_refusal_served_by_the_host_rotation(pkg, gates):
+    """convrot=True: group-size check as in the reference, then the rotation goes to the
+    host's helper (counted under `convrot`) and the rotated activation enters the gated path."""
+    lin = pkg.linear
+    x = torch.ones((4, 512), dtype=torch.bfloat16)
+    w = torch.ones((8, 512), dtype=torch.int8)
+    ws = torch.ones((8,))
+    with pytest.raises(ValueError, match="ConvRot group size 384 does not divide input features 512"):
+        lin.int8_linear(x, w, ws, convrot=True, convrot_groupsize=384, gates=gates)
+    with pytest.raises(RuntimeError, match="no 'convrot_rotate' fallback"):
+        lin.int8_linear(x, w, ws, convrot=True, gates=gates)
+    seen = []
+
+    class Stop(Exception):
+        pass
+
+    def quantize(x2d, stochastic_rounding=0):
+        seen.append(("quantize", tuple(x2d.shape), float(x2d[0, 0])))
+        raise Stop
+
+    gates.register_fallbacks(convrot_rotate=lambda t, group: seen.append(("rotate", group)) or t * 2,
+                             quantize=quantize)
+    with pytest.raises(Stop):
+        lin.int8_linear(x, w, ws, convrot=True, convrot_groupsize=256, gates=gates)
+    assert seen == [("rotate", 256), ("quantize", (4, 512), 2.0)]
+    assert gates.dump_counters()["convrot"]["reasons"] == {"convrot": 2}
+
+
+def test_audit_table_is_parsed_once_until_it_changes(pkg, tmp_path, monkeypatch):
+    import shutil
+    so = tmp_path / "libcopy2.so"
+    shutil.copy(pkg._lib.so_path(), so)
+    monkeypatch.setenv("B2DIT_SO", str(so))
+    monkeypatch.setattr(pkg._lib, "_lib", None)
+    pkg._lib.load()
+    pkg._lib.admit(so, note="test")
+    reads = []
+    real = json.loads
+    monkeypatch.setattr(pkg._lib.json, "loads", lambda text: reads.append(1) or real(text))
+    assert all(pkg._lib.audited("flash_fwd") for _ in range(50))
+    assert len(reads) == 1
+    pkg._lib.refresh_audit()
+    assert pkg._lib.audited() and len(reads) == 2
+    monkeypatch.undo()
+    monkeypatch.setattr(pkg._lib, "_lib", None)
+    pkg._lib.refresh_audit()
+    pkg._lib.load()
+
+
 def test_head_chunk_choice_fills_the_last_wave():
     """23638 tokens give 93 CTAs per head: one head per launch would leave 55 of 148 SMs idle,
     so fewer, larger chunks are chosen; 109099 tokens (427 CTAs per head) keep the most chunks."""

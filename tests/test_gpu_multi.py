@@ -85,12 +85,17 @@ def _worker(rank, world, port, seq, result_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("seq", [1001, 4099])
+def _largest_world(n: int) -> int:
+    """The largest sequence-parallel degree of the deployment (8, 4, 2) the box can run."""
+    return max(w for w in (8, 4, 2) if w <= n)
+
+
+@pytest.mark.parametrize("seq", [1001, 4099, 23638])
 def test_ulysses_attention_and_block_bitwise_vs_single_gpu(tmp_path, seq):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    world = 4 if n >= 4 else 2
+    world = _largest_world(n)
     port = _free_port()
     mp.spawn(_worker, args=(world, port, seq, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
@@ -102,3 +107,33 @@ def test_ulysses_attention_and_block_bitwise_vs_single_gpu(tmp_path, seq):
         psnr = float(text.split("psnr=")[1])
         assert psnr >= 60.0, text
         assert "block_equal=True" in text, text
+
+
+def test_second_device_in_the_same_process(cuda_pkg, ref):
+    """One process, two GPUs: the first launch of each tensor-core kernel on cuda:1 comes after
+    cuda:0 has already been set up.  The launch set-up (shared-memory opt-in, cluster occupancy,
+    SM count) is per device, so both devices must give the oracle's bits."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    ops = cuda_pkg.ops
+    g = torch.Generator().manual_seed(21)
+    # one shape for the single-CTA GEMM (M < 256) and one for the CTA-pair kernel
+    cases = []
+    for m, k, n in ((200, 512, 264), (600, 1024, 520)):
+        x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+        wq, ws = ref.quantize_weight_per_channel(torch.randn((n, k), generator=g) * 0.02)
+        bias = (torch.randn((n,), generator=g) * 0.01).to(torch.bfloat16)
+        cases.append((x, wq, ws, bias, ref.int8_linear(x, wq, ws, bias)))
+    s, h = 333, 2
+    q, kk, v = (torch.randn((s, h, 128), generator=g).to(torch.bfloat16) for _ in range(3))
+    view = lambda t: t.transpose(0, 1).unsqueeze(0)
+    want_o = ref.attention_fp32(view(q), view(kk), view(v), 128 ** -0.5)
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        for x, wq, ws, bias, want in cases:
+            got = ops.int8_linear(x.to(dev), wq.to(dev), ws.to(dev), bias.to(dev))
+            assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16)), dev
+        got_o = ops.fwd_bhsd(view(q.to(dev)), view(kk.to(dev)), view(v.to(dev)), 128 ** -0.5)
+        err = float((got_o.float().cpu() - want_o).abs().max())
+        assert err <= max(2e-4, 2.0 ** -7 * float(want_o.abs().max())), (dev, err)
+        with torch.cuda.device(dev):
+            ops.check_device_status(torch.device(dev))
