@@ -10,30 +10,31 @@
 //
 //   One CTA owns TWO 128-row query tiles of one (batch, head) and walks the KV
 //   sequence in 128-row steps.
-//     warps 0-7    softmax for query tile 0, TWO threads per row: warp w and warp w+4
-//                  read the same 32 tensor-memory lanes and split the 128 S columns
-//                  64/64, so two instruction streams share each scheduler and the
-//                  exp2 unit stays busy while either one is blocked
-//     warps 8-15   the same for query tile 1
-//     warp 16      MMA issuer: S = Q.K^T (tcgen05.mma kind::f16, operands in shared
+//     warps 0-3    softmax for query tile 0, ONE thread per row: warp w reads the 32
+//                  tensor-memory lanes of its quarter and keeps all 128 scores of its row in
+//                  registers, so the row maximum and the row sum need no exchange between
+//                  threads
+//     warps 4-7    the same for query tile 1
+//     warp 8       MMA issuer: S = Q.K^T (tcgen05.mma kind::f16, operands in shared
 //                  memory) and O += P.V (P read from tensor memory, V from shared
 //                  memory as an MN-major operand); accumulators S0,S1,O0,O1 fill the
 //                  512 tensor-memory columns
-//     warp 17      TMA loader: Q once, K and V tiles through a two-stage ring
+//     warp 9       TMA loader: Q once, K and V tiles through a two-stage ring
 //                  (128-byte swizzle; plain per-CTA loads, no multicast)
-//     warps 18-19  idle; they complete the service warpgroup, which hands most of its
-//                  registers to the softmax warpgroups (setmaxnreg: 32 vs 112 per thread)
+//     warps 10-11  idle; they complete the service warpgroup, which hands most of its
+//                  registers to the softmax warpgroups (setmaxnreg)
 //   The two tiles ping-pong: while one tile's softmax runs, the tensor core works on
 //   the other tile's MMAs.  P overwrites S in place as bf16.
-//   Per step a thread loads its 64 scores, the two threads of a row exchange their maxima
-//   (shared memory + a 64-thread named barrier) and raise the running max, rescaling O
-//   and l, only when it lags by more than 2^8 in the exp2 domain (rare after the first
-//   steps; the final O/l is exact either way).  The scale-and-subtract and the row sum run
-//   as packed f32x2 instructions: the softmax warps are bound by instruction issue, not by
-//   the exp2 unit (moving a share of the exponentials to a polynomial on the FMA pipe was
-//   measured slower at every share).  P is published in two column halves, each
-//   with its own mbarrier, so the tensor core starts O += P.V on the first half while the
-//   second half is still being exponentiated.
+//   The exp2 unit delivers 16 results per clock per SM: 1024 clocks for a 128x128 tile, which
+//   is exactly the time of the tile's two MMAs, so with every exponential on that unit the
+//   softmax can at best tie with the tensor core.  A fixed share of the score pairs therefore
+//   takes its exponential on the FMA pipe (2^floor(x) times a cubic in the fraction, relative
+//   error 8.7e-5, a twentieth of the bf16 rounding P gets next), and the two pipes work side
+//   by side.  The running max is raised, rescaling O and l, only when it lags by more than
+//   2^8 in the exp2 domain (rare after the first steps; the final O/l is exact either way).
+//   The scale-and-subtract and the row sum run as packed f32x2 instructions.  P is published
+//   in column groups, each with its own mbarrier, so the tensor core starts O += P.V on the
+//   first group while the later ones are still being exponentiated.
 // Every mbarrier wait is bounded; on a timeout the kernel records a status word and
 // returns through the common teardown.
 #include <cmath>
@@ -54,35 +55,45 @@ constexpr int HEAD_DIM = 128;
 constexpr int HALF_BYTES = 128 * 128;        // one [128 rows x 64 bf16] swizzled half tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
 constexpr int KV_STAGES = 2;
-constexpr int kFirstSoftmaxWarp = 0, kMmaWarp = 16, kLoadWarp = 17;   // warps 18, 19 idle
-constexpr int NUM_THREADS = (16 + 4) * 32;   // 640: four softmax warpgroups + one service warpgroup
+constexpr int kSoftmaxWarps = 8, kMmaWarp = 8, kLoadWarp = 9;   // warps 10, 11 idle
+constexpr int NUM_THREADS = (kSoftmaxWarps + 4) * 32;   // 384: two softmax warpgroups + one service warpgroup
 #ifndef B2_FLASH_REGS_SOFTMAX
-#define B2_FLASH_REGS_SOFTMAX 112
+#define B2_FLASH_REGS_SOFTMAX 232
 #endif
 #ifndef B2_FLASH_REGS_SERVICE
 #define B2_FLASH_REGS_SERVICE 32
 #endif
+// P is published to the MMA issuer in this many column groups per step (2 or 4)
+#ifndef B2_FLASH_P_PARTS
+#define B2_FLASH_P_PARTS 2
+#endif
+// Which of the 8 score pairs of a 16-column chunk take their exponential on the FMA pipe
+// (bit i = pair i) instead of the exp2 unit.
+#ifndef B2_FLASH_EMU_MASK
+#define B2_FLASH_EMU_MASK 0x88
+#endif
 // setmaxnreg.inc waits, without a limit, until the registers it asks for are free in the
 // CTA's own allocation, so the split must fit into what the kernel was launched with:
-// per scheduler, four softmax warps and one service warp share five launch allocations.
+// per scheduler, two softmax warps and one service warp share three launch allocations.
 // The launcher checks this against the compiled register count before every first launch.
-constexpr int kLaunchRegs = 96;   // 65536 / 640 threads, rounded down to the allocation unit of 8
-static_assert(4 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE <= 5 * kLaunchRegs,
+constexpr int kLaunchRegs = 168;   // 65536 / 384 threads, rounded down to the allocation unit of 8
+static_assert(2 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE <= 3 * kLaunchRegs,
               "register split exceeds the CTA's launch allocation");
+constexpr int P_PARTS = B2_FLASH_P_PARTS;
+static_assert(P_PARTS == 2 || P_PARTS == 4, "P is published in halves or quarters");
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 384;
 
 constexpr int SMEM_Q = 0;                                   // 2 tiles
 constexpr int SMEM_K = SMEM_Q + 2 * TILE_BYTES;             // KV_STAGES tiles
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;     // KV_STAGES tiles
-constexpr int SMEM_BARS = SMEM_V + KV_STAGES * TILE_BYTES;  // 16 mbarriers + tmem slot + abort
-constexpr int NUM_BARS = 18;
-constexpr int SMEM_XCHG = SMEM_BARS + NUM_BARS * 8 + 16;    // row exchange floats [2 tiles][2 halves][128 rows]
-constexpr int SMEM_TOTAL = 1024 + SMEM_XCHG + 2 * 2 * 128 * 4;
+constexpr int SMEM_BARS = SMEM_V + KV_STAGES * TILE_BYTES;  // mbarriers + tmem slot + abort
+constexpr int NUM_BARS = 14 + 2 * P_PARTS;
+constexpr int SMEM_TOTAL = 1024 + SMEM_BARS + NUM_BARS * 8 + 16;
 
-// mbarrier indices
-enum { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, P_FULL = 12,
-       O_FULL = 14, PB_FULL = 16 /* second column half of P, per tile */ };
+// mbarrier indices (two of each: ring stage or query tile); P_PART + 2*part + tile
+enum { Q_FULL = 0, K_FULL = 2, K_EMPTY = 4, V_FULL = 6, V_EMPTY = 8, S_FULL = 10, O_FULL = 12,
+       P_PART = 14 };
 
 struct FlashArgs {
   __nv_bfloat16* out;  // [B, S, H, 128]
@@ -121,6 +132,71 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// 2^x for a packed pair on the FMA pipe.  x <= 8 by construction of the running max (larger
+// values never reach an exponential); x < -127 (and -inf of masked columns) gives exactly 0;
+// NaN stays NaN.
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t xx) {
+  float x0, x1;
+  unpack2(xx, x0, x1);
+  asm("max.NaN.f32 %0, %0, 0fC2FE0000;" : "+f"(x0));   // max(x, -127), NaN kept
+  asm("max.NaN.f32 %0, %0, 0fC2FE0000;" : "+f"(x1));
+  const uint64_t xc = pack2(x0, x1);
+  const uint64_t magic = pack2(12582912.0f, 12582912.0f);   // 1.5 * 2^23
+  uint64_t j, jf, f;
+  // round DOWN: the low mantissa bits of j hold floor(x) (two's complement)
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(j) : "l"(xc), "l"(magic));
+  asm("sub.rn.ftz.f32x2 %0, %1, %2;" : "=l"(jf) : "l"(j), "l"(magic));
+  asm("sub.rn.ftz.f32x2 %0, %1, %2;" : "=l"(f) : "l"(xc), "l"(jf));   // x - floor(x), in [0, 1)
+  uint64_t q = fma2(pack2(0.07706984132528305f, 0.07706984132528305f), f,
+                    pack2(0.22764800488948822f, 0.22764800488948822f));
+  q = fma2(q, f, pack2(0.6951131224632263f, 0.6951131224632263f));
+  q = fma2(q, f, pack2(1.0f, 1.0f));
+  // 2^floor(x) built in the exponent field; floor(x) = -127 gives 0
+  float j0, j1;
+  unpack2(j, j0, j1);
+  const uint32_t s0 = (__float_as_uint(j0) << 23) + 0x3f800000u;
+  const uint32_t s1 = (__float_as_uint(j1) << 23) + 0x3f800000u;
+  return mul2(q, pack2(__uint_as_float(s0), __uint_as_float(s1)));
+}
+
+// One pair of scores -> exponentials (added to a running packed sum) -> packed bf16.
+template <bool POLY>
+__device__ __forceinline__ uint32_t exp_pair(uint32_t sa, uint32_t sb, uint64_t sl2x2, uint64_t nmsx2,
+                                             uint64_t& sum2) {
+  const uint64_t xx = fma2(pack2(__uint_as_float(sa), __uint_as_float(sb)), sl2x2, nmsx2);
+  float e0, e1;
+  if constexpr (POLY) {
+    const uint64_t ee = ex2_poly2(xx);
+    sum2 = add2(sum2, ee);
+    unpack2(ee, e0, e1);
+  } else {
+    float x0, x1;
+    unpack2(xx, x0, x1);
+    e0 = ex2_approx(x0);
+    e1 = ex2_approx(x1);
+    sum2 = add2(sum2, pack2(e0, e1));
+  }
+  return pack_bf16x2_rn(e0, e1);
+}
+
+// 16 scores of one thread (one chunk) -> 8 packed bf16 probabilities.
+__device__ __forceinline__ void exp_chunk(const uint32_t* s, uint32_t (&p)[8], uint64_t sl2x2,
+                                          uint64_t nmsx2, uint64_t (&sm2)[4]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if ((B2_FLASH_EMU_MASK >> i) & 1)
+      p[i] = exp_pair<true>(s[2 * i], s[2 * i + 1], sl2x2, nmsx2, sm2[i & 3]);
+    else
+      p[i] = exp_pair<false>(s[2 * i], s[2 * i + 1], sl2x2, nmsx2, sm2[i & 3]);
+  }
+}
+
 // rows x 64-element half tiles of one [128 x 128] bf16 tile
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                           int row0, int h, int b, int swap) {
@@ -146,7 +222,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile float* xchg = reinterpret_cast<volatile float*>(smem + SMEM_XCHG);  // [2][2][128]
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int idx) -> uint32_t { return bar0 + idx * 8; };
@@ -158,7 +233,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i)
-      mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1 || i >= PB_FULL) ? 8 : 1);
+      mbar_init(bar(i), i >= P_PART ? 4 : 1);   // P groups: one arrival per softmax warp of the tile
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -175,7 +250,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   // Registers move from the service warpgroup (MMA issuer, loader, two idle warps) to the
-  // softmax warpgroups: each scheduler holds four softmax warps and one service warp.
+  // softmax warpgroups: each scheduler holds two softmax warps and one service warp.
   if (warp >= kMmaWarp) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(B2_FLASH_REGS_SERVICE));
   if (warp == kLoadWarp) {
@@ -216,16 +291,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       auto issue_qk = [&](uint32_t d, uint32_t q_lo, uint32_t k_lo) {
         if (leader) mma_f16_ss_kmajor_x8(d, q_lo, k_lo, kIdescQK);
       };
-      // O += P.V for one published column half of P (group 0: kv rows [0,32) and [64,96),
-      // MMAs 0,1,4,5 of the natural order; group 1: the rest).  P: 8 tensor-memory columns
-      // (16 bf16 of kv) per MMA; V: MN-major, 16 kv rows = 2048 bytes per MMA.
-      auto issue_pv = [&](uint32_t d, uint32_t p_base, uint32_t v_lo, const int group, uint32_t acc) {
+      // O += P.V for one published column group of P (kv rows [part*128/P_PARTS, ...)).  P: 8
+      // tensor-memory columns (16 bf16 of kv) per MMA; V: MN-major, 16 kv rows = 2048 bytes
+      // per MMA.
+      auto issue_pv = [&](uint32_t d, uint32_t p_base, uint32_t v_lo, const int part, uint32_t acc) {
         if (leader) {
-          if (group == 0)
-            mma_f16_ts_x4<0>(d, p_base, v_lo, kIdescPV, acc);
-          else
-            mma_f16_ts_x4<2>(d, p_base, v_lo, kIdescPV, acc);
+          if constexpr (P_PARTS == 2) {
+            if (part == 0)
+              mma_f16_ts_seq<0, 4>(d, p_base, v_lo, kIdescPV, acc);
+            else
+              mma_f16_ts_seq<4, 4>(d, p_base, v_lo, kIdescPV, acc);
+          } else {
+            if (part == 0)
+              mma_f16_ts_seq<0, 2>(d, p_base, v_lo, kIdescPV, acc);
+            else if (part == 1)
+              mma_f16_ts_seq<2, 2>(d, p_base, v_lo, kIdescPV, acc);
+            else if (part == 2)
+              mma_f16_ts_seq<4, 2>(d, p_base, v_lo, kIdescPV, acc);
+            else
+              mma_f16_ts_seq<6, 2>(d, p_base, v_lo, kIdescPV, acc);
+          }
         }
+      };
+      // all column groups of one tile's P, each as soon as it is published
+      auto pv_tile = [&](const int t, uint32_t d, uint32_t p_base, uint32_t v_lo, const int j) -> bool {
+#pragma unroll
+        for (int part = 0; part < P_PARTS; ++part) {
+          if (!mbar_wait(bar(P_PART + 2 * part + t), j & 1, abort_flag, kStatusFlashTimeout)) return false;
+          tc_fence_after();
+          issue_pv(d, p_base, v_lo, part, (part != 0 || j != 0) ? 1u : 0u);
+        }
+        return true;
       };
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, kStatusFlashTimeout) &&
                 mbar_wait(bar(K_FULL), 0, abort_flag, kStatusFlashTimeout);
@@ -245,12 +341,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       auto step = [&](const int j, const uint32_t vd, const uint32_t kd_next, const int st) -> bool {
         const bool last = j + 1 == n_kv;
         const int st2 = st ^ 1;
-        if (!mbar_wait(bar(P_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
-        tc_fence_after();
-        issue_pv(o0, s0, vd, 0, j != 0);
-        if (!mbar_wait(bar(PB_FULL), j & 1, abort_flag, kStatusFlashTimeout)) return false;
-        tc_fence_after();
-        issue_pv(o0, s0, vd, 1, 1);
+        if (!pv_tile(0, o0, s0, vd, j)) return false;
         if (last) {
           if (leader) tc_commit(bar(O_FULL));
         } else {
@@ -259,12 +350,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           issue_qk(s0, q0, kd_next);
           if (leader) tc_commit(bar(S_FULL));
         }
-        if (!mbar_wait(bar(P_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
-        tc_fence_after();
-        issue_pv(o1, s1, vd, 0, j != 0);
-        if (!mbar_wait(bar(PB_FULL + 1), j & 1, abort_flag, kStatusFlashTimeout)) return false;
-        tc_fence_after();
-        issue_pv(o1, s1, vd, 1, 1);
+        if (!pv_tile(1, o1, s1, vd, j)) return false;
         if (leader) tc_commit(bar(V_EMPTY + st));
         if (last) {
           if (leader) tc_commit(bar(O_FULL + 1));
@@ -288,63 +374,38 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(B2_FLASH_REGS_SOFTMAX));
-    // ---------------- softmax + output: two threads per row, 64 columns each ----------------
-    const int ws = warp - kFirstSoftmaxWarp;
-    const int t = ws >> 3;              // query tile
-    const int half = (ws >> 2) & 1;     // which 64 of the 128 S / O columns
+    // ---------------- softmax + output: one thread per row, all 128 columns ----------------
+    const int t = warp >> 2;            // query tile
     const int quarter = warp & 3;       // tensor-memory lane quarter of this warp
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem_base + (t ? COL_S1 : COL_S0) + lane_sel + half * 64;
-    const uint32_t p_tmem = tmem_base + (t ? COL_S1 : COL_S0) + lane_sel + half * 32;
-    const uint32_t o_tmem = tmem_base + (t ? COL_O1 : COL_O0) + lane_sel + half * 64;
-    // The two warps that share a row group meet at a named barrier (bar.sync id, 64).
-    // bar.sync has no time limit, so the loop below never leaves early: after an abort a
-    // warp keeps walking the remaining steps, skips the mbarrier waits, and still executes
-    // the one barrier per step (and the one after the loop) that its partner executes.
-    const uint32_t pair_bar = 1 + t * 4 + quarter;
+    const uint32_t s_tmem = tmem_base + (t ? COL_S1 : COL_S0) + lane_sel;
+    const uint32_t p_tmem = s_tmem;     // P (64 columns of packed bf16) overwrites the first half of S
+    const uint32_t o_tmem = tmem_base + (t ? COL_O1 : COL_O0) + lane_sel;
     bool ok = true;
-    auto pair_sync = [&]() { named_barrier_sync(pair_bar, 64); };
-    volatile float* my_x = xchg + (t * 2 + half) * 128 + row_in_tile;
-    volatile float* other_x = xchg + (t * 2 + (half ^ 1)) * 128 + row_in_tile;
     const float sl2 = args.scale_log2;
     const int tail_valid = args.S - (n_kv - 1) * BLOCK_N;  // valid columns of the last step
-    float row_max = -INFINITY;  // raw-score domain, identical in both threads of the row
-    float row_sum = 0.f;        // this thread's 64 columns only
+    float row_max = -INFINITY;  // raw-score domain
+    float row_sum = 0.f;
     for (int j = 0; j < n_kv; ++j) {
       if (ok) ok = mbar_wait(bar(S_FULL + t), j & 1, abort_flag, kStatusFlashTimeout);
       tc_fence_after();
-      // this thread's 64 scores -> registers
-      uint32_t s[64];
-      {
-        uint32_t(&c0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[0]);
-        uint32_t(&c1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[16]);
-        uint32_t(&c2)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[32]);
-        uint32_t(&c3)[16] = *reinterpret_cast<uint32_t(*)[16]>(&s[48]);
-        tmem_ld_32x32b_x16(s_tmem + 0, c0);
-        tmem_ld_32x32b_x16(s_tmem + 16, c1);
-        tmem_ld_32x32b_x16(s_tmem + 32, c2);
-        tmem_ld_32x32b_x16(s_tmem + 48, c3);
-        tmem_wait_ld();
-      }
-      // columns of this thread that are valid in this step (tail masking)
-      const int valid = ((j + 1 == n_kv) ? tail_valid : BLOCK_N) - half * 64;
-      if (valid < 64) {
+      // the row's 128 scores -> registers
+      uint32_t s[128];
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
-          if (c >= valid) s[c] = 0xff800000u;  // -inf
+      for (int c = 0; c < 128; c += 32) tmem_ld_32x32b_x32(s_tmem + c, *reinterpret_cast<uint32_t(*)[32]>(&s[c]));
+      tmem_wait_ld();
+      if (j + 1 == n_kv && tail_valid < BLOCK_N) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (c >= tail_valid) s[c] = 0xff800000u;  // -inf
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; c += 2)
+      for (int c = 0; c < 128; c += 2)
         mx[(c >> 1) & 3] = fmax3(mx[(c >> 1) & 3], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-      const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      // the row's max over all 128 columns: exchange with the partner thread.  After the
-      // barrier both threads have also finished READING S, so P may overwrite it.
-      *my_x = my_max;
-      pair_sync();
-      const float m_row = fmaxf(my_max, *other_x);
-      // lazy raise: identical decision in both threads of the row (true on the first step)
+      const float m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // lazy raise (always on the first step)
       const bool raise = (m_row - row_max) * sl2 > 8.0f;
       float alpha = 1.0f;
       if (raise) {
@@ -354,7 +415,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       if (j != 0 && __any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-        for (int c = 0; c < 64; c += 16) {
+        for (int c = 0; c < 128; c += 16) {
           uint32_t o[16];
           tmem_ld_32x32b_x16(o_tmem + c, o);
           tmem_wait_ld();
@@ -367,25 +428,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // exponentials on packed pairs: one f32x2 FMA and one f32x2 add per two scores
       const uint64_t sl2x2 = pack2(sl2, sl2), nmsx2 = pack2(neg_ms, neg_ms);
       uint64_t sm2[4] = {0ull, 0ull, 0ull, 0ull};
-      // two column halves of 32 scores, each published as soon as it is written
+      // eight chunks of 16 scores -> 8 columns of packed bf16 each; a column group is published
+      // as soon as it is written
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t p[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const uint64_t xx = fma2(pack2(__uint_as_float(s[32 * hh + c]), __uint_as_float(s[32 * hh + c + 1])),
-                                   sl2x2, nmsx2);
-          float x0, x1;
-          unpack2(xx, x0, x1);
-          const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
-          sm2[(c >> 1) & 3] = add2(sm2[(c >> 1) & 3], pack2(e0, e1));
-          p[c >> 1] = pack_bf16x2_rn(e0, e1);
+      for (int q = 0; q < 8; ++q) {
+        uint32_t p[8];
+        exp_chunk(&s[16 * q], p, sl2x2, nmsx2, sm2);
+        tmem_st_32x32b_x8(p_tmem + 8 * q, p);
+        if ((q + 1) % (8 / P_PARTS) == 0) {
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(P_PART + 2 * (q / (8 / P_PARTS)) + t));  // one arrival per warp
         }
-        tmem_st_32x32b_x16(p_tmem + 16 * hh, p);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar((hh ? PB_FULL : P_FULL) + t));  // one arrival per warp, 8 per tile
       }
       {
         float a0, a1, b0, b1, c0, c1, d0, d1;
@@ -396,19 +451,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         row_sum += ((a0 + a1) + (b0 + b1)) + ((c0 + c1) + (d0 + d1));
       }
     }
-    // ---- final: O / l -> bf16 -> global (BSHD); l = both halves' sums ----
+    // ---- final: O / l -> bf16 -> global (BSHD) ----
     if (ok) ok = mbar_wait(bar(O_FULL + t), 0, abort_flag, kStatusFlashTimeout);
-    *my_x = row_sum;
-    pair_sync();
     if (ok) {
       tc_fence_after();
-      const float l = row_sum + *other_x;
+      const float l = row_sum;
       const int row = (pair * 2 + t) * BLOCK_M + row_in_tile;
       const float inv = (l == 0.f || l != l) ? 1.0f : 1.0f / l;
-      __nv_bfloat16* dst =
-          args.out + (((int64_t)b * args.S + row) * args.H + h) * (int64_t)HEAD_DIM + half * 64;
+      __nv_bfloat16* dst = args.out + (((int64_t)b * args.S + row) * args.H + h) * (int64_t)HEAD_DIM;
 #pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
+      for (int c = 0; c < 128; c += 32) {
         uint32_t o[32];
         tmem_ld_32x32b_x32(o_tmem + c, o);
         tmem_wait_ld();
@@ -517,7 +569,7 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int
     cudaFuncAttributes fa;
     e = cudaFuncGetAttributes(&fa, flash_fwd_kernel);
     if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "flash_fwd: attributes: %s", cudaGetErrorString(e));
-    if (4 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE > 5 * ((fa.numRegs + 7) / 8 * 8))
+    if (2 * B2_FLASH_REGS_SOFTMAX + B2_FLASH_REGS_SERVICE > 3 * ((fa.numRegs + 7) / 8 * 8))
       return fail(B2_LAUNCH_FAILED, "flash_fwd: register split %d/%d does not fit %d launch registers",
                   B2_FLASH_REGS_SOFTMAX, B2_FLASH_REGS_SERVICE, fa.numRegs);
     return B2_OK;

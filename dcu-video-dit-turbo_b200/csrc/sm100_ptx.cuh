@@ -206,6 +206,53 @@ __device__ __forceinline__ void mma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, 
       : "memory");
 }
 
+// COUNT (2 or 4) MMAs with A in tensor memory over CONSECUTIVE 16-element slices of K:
+// MMA i reads A at a_tmem + (M0+i)*8 columns and B at b_lo + (M0+i)*128 descriptor units.
+// `accumulate` applies to the first MMA; the others always accumulate.
+template <int M0, int COUNT>
+__device__ __forceinline__ void mma_f16_ts_seq(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                               uint32_t idesc, uint32_t accumulate) {
+  static_assert(COUNT == 2 || COUNT == 4, "two or four MMAs per batch");
+  if constexpr (COUNT == 4) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p0, p1;\n\t"
+        ".reg .b64 db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p0, %5, 0;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "add.u32 ra, %1, %6; add.u32 rb, %2, %7; mov.b64 db, {rb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p0;\n\t"
+        "add.u32 ra, %1, %8; add.u32 rb, %2, %9; mov.b64 db, {rb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+        "add.u32 ra, %1, %10; add.u32 rb, %2, %11; mov.b64 db, {rb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+        "add.u32 ra, %1, %12; add.u32 rb, %2, %13; mov.b64 db, {rb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+        "}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(accumulate), "n"(M0 * 8),
+        "n"(M0 * 128), "n"((M0 + 1) * 8), "n"((M0 + 1) * 128), "n"((M0 + 2) * 8), "n"((M0 + 2) * 128),
+        "n"((M0 + 3) * 8), "n"((M0 + 3) * 128)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p0, p1;\n\t"
+        ".reg .b64 db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p0, %5, 0;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "add.u32 ra, %1, %6; add.u32 rb, %2, %7; mov.b64 db, {rb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p0;\n\t"
+        "add.u32 ra, %1, %8; add.u32 rb, %2, %9; mov.b64 db, {rb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p1;\n\t"
+        "}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(accumulate), "n"(M0 * 8),
+        "n"(M0 * 128), "n"((M0 + 1) * 8), "n"((M0 + 1) * 128)
+        : "memory");
+  }
+}
+
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -248,6 +295,13 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
       : "memory");
 }
 
