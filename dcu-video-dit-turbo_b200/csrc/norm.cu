@@ -18,44 +18,6 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <int TPR>
-__device__ __forceinline__ float row_allreduce_sum(float v, float* smem) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  if constexpr (TPR > 32) {
-    constexpr int WPR = TPR / 32;
-    const int warp = threadIdx.x >> 5;
-    __syncthreads();  // previous use of smem is complete
-    if ((threadIdx.x & 31) == 0) smem[warp] = v;
-    __syncthreads();
-    const int first = (warp / WPR) * WPR;
-    float s = smem[first];
-#pragma unroll
-    for (int i = 1; i < WPR; ++i) s += smem[first + i];
-    v = s;
-  }
-  return v;
-}
-
-template <int TPR>
-__device__ __forceinline__ float row_allreduce_nanmax(float v, float* smem) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v = nanmax(v, __shfl_xor_sync(0xffffffffu, v, off));
-  if constexpr (TPR > 32) {
-    constexpr int WPR = TPR / 32;
-    const int warp = threadIdx.x >> 5;
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) smem[warp] = v;
-    __syncthreads();
-    const int first = (warp / WPR) * WPR;
-    float s = smem[first];
-#pragma unroll
-    for (int i = 1; i < WPR; ++i) s = nanmax(s, smem[first + i]);
-    v = s;
-  }
-  return v;
-}
-
 // One row per TPR threads, VPT vectors of 8 bf16 per thread; C % 8 == 0,
 // C <= TPR*VPT*8.  QUANT selects the fused quantizer output.
 template <int TPR, int VPT, bool QUANT>
@@ -64,7 +26,7 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
                      const uint4* __restrict__ shift, uint4* __restrict__ out_bf16,
                      uint2* __restrict__ out_q, float* __restrict__ out_scale, int64_t M, int cvec,
                      float inv_c, float eps) {
-  __shared__ float red[kThreads / 32];
+  __shared__ float red[3][kThreads / 32];   // one buffer per reduction of a row (slot_allreduce)
   // per-column operands staged once per CTA: factor = bf16(1+scale) and shift, packed
   // like the data (8 bf16 per uint4)
   extern __shared__ uint4 colvec[];
@@ -106,33 +68,49 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
         }
       }
     }
-    // the row is unpacked to fp32 once and stays in registers for all three passes
-    float xf[VPT][8];
-    float sum = 0.f;
+    // the row is unpacked once, to packed fp32 pairs, and stays in registers for all three
+    // passes; sums, differences, squares and the scaling are packed f32x2 instructions
+    uint64_t xf[VPT][4];
+    uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        xf[i][2 * j] = bf16lo_to_f32(w[j]);
-        xf[i][2 * j + 1] = bf16hi_to_f32(w[j]);
-        sum += xf[i][2 * j] + xf[i][2 * j + 1];
+        xf[i][j] = bf16x2_to_f32x2(w[j]);
+        sum2[j & 1] = add2(sum2[j & 1], xf[i][j]);
       }
     }
-    const float mean = row_allreduce_sum<TPR>(sum, red) * inv_c;
-    float sq = 0.f;
+    float sum;
+    {
+      float a0, a1, b0, b1;
+      unpack2(sum2[0], a0, a1);
+      unpack2(sum2[1], b0, b1);
+      sum = (a0 + a1) + (b0 + b1);
+    }
+    const float mean = slot_allreduce<kThreads, TPR>(sum, red[0], slot, SumOp()) * inv_c;
+    const uint64_t mean2 = pack2(mean, mean);
+    uint64_t sq2[2] = {0ull, 0ull};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + i * TPR;
       if (c < cvec) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a = xf[i][2 * j] - mean, b = xf[i][2 * j + 1] - mean;
-          sq += a * a + b * b;
+          xf[i][j] = sub2(xf[i][j], mean2);          // kept: the normalisation reuses x - mean
+          sq2[j & 1] = fma2(xf[i][j], xf[i][j], sq2[j & 1]);
         }
       }
     }
-    const float rstd = rsqrtf(row_allreduce_sum<TPR>(sq, red) * inv_c + eps);
+    float sq;
+    {
+      float a0, a1, b0, b1;
+      unpack2(sq2[0], a0, a1);
+      unpack2(sq2[1], b0, b1);
+      sq = (a0 + a1) + (b0 + b1);
+    }
+    const float rstd = rsqrtf(slot_allreduce<kThreads, TPR>(sq, red[1], slot, SumOp()) * inv_c + eps);
+    const uint64_t rstd2 = pack2(rstd, rstd);
     uint32_t acc = 0;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -143,21 +121,22 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const uint32_t n = pack_bf16x2_rn((xf[i][2 * j] - mean) * rstd, (xf[i][2 * j + 1] - mean) * rstd);
+          const uint32_t n = f32x2_to_bf16x2_rn(mul2(xf[i][j], rstd2));
           // The two modulation roundings as packed bf16 instructions on the FMA pipe.  Each is
           // the correctly rounded product / sum of two bf16 values, which is what the fp32
           // formulation computes too: the fp32 product of two bf16 is exact, and the fp32 sum
           // of two bf16 is exact unless their exponents lie more than 16 apart, where the small
           // term is far below half an ulp in either formulation.
           w[j] = bf16x2_add_rn(bf16x2_mul_rn(n, fcw[j]), shw[j]);
-          if (QUANT) acc = absmax_bf16x2(acc, w[j]);
+          // the chain starts from data: vector 0 is live in every thread that holds any
+          if (QUANT) acc = (i == 0 && j == 0) ? w[j] : absmax_bf16x2(acc, w[j]);
         }
         v[i] = make_uint4(w[0], w[1], w[2], w[3]);
         if (!QUANT && live) out_bf16[row * cvec + c] = v[i];
       }
     }
     if constexpr (QUANT) {
-      const float absmax = row_allreduce_nanmax<TPR>(fold_absmax(acc), red);
+      const float absmax = slot_allreduce<kThreads, TPR>(fold_absmax(acc), red[2], slot, NanMaxOp());
       float r;
       bool zero_row;
       const float s = row_scale_from_absmax(absmax, &r, &zero_row);
@@ -173,104 +152,120 @@ layernorm_mod_kernel(const uint4* __restrict__ x, const uint4* __restrict__ scal
   }
 }
 
-// qkv bf16 [S,3,H,128]; 16 threads per (row, part in {q,k}, head), 8 elements each.
+// RMSNorm + rotary embedding for the 8 channels one thread holds of a 128-channel head; the
+// 16 threads of the head (a half-warp: lanes `group_mask`) reduce the sum of squares.
+// Shared by the in-place and the packing kernel, so both give the same bits.
+__device__ __forceinline__ uint4 norm_rope_vec8(const uint4 v, const uint4 wv, const float4 c,
+                                                const float4 sn, float eps, uint32_t group_mask) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+  uint64_t e2[4];
+  uint64_t ss2 = 0ull;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    e2[j] = bf16x2_to_f32x2(w[j]);
+    ss2 = fma2(e2[j], e2[j], ss2);
+  }
+  float s0, s1;
+  unpack2(ss2, s0, s1);
+  float ss = s0 + s1;
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(group_mask, ss, off);
+  const float rms = rsqrtf(ss * (1.0f / 128.0f) + eps);
+  const uint64_t rms2 = pack2(rms, rms);
+  const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float y0, y1;
+    unpack2(mul2(mul2(e2[j], rms2), bf16x2_to_f32x2(ww[j])), y0, y1);   // (x * rms) * w
+    o[j] = pack_bf16x2_rn(__fmaf_rn(y0, cc[j], -__fmul_rn(y1, sv[j])),
+                          __fmaf_rn(y1, cc[j], __fmul_rn(y0, sv[j])));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+constexpr int kRopeMaxIter = 6;   // 16-byte vectors of one row per thread (template ITER): heads <= 32
+
+// qkv bf16 [S,3,H,128], q and k normed and rotated in place.  One CTA walks rows; a thread
+// keeps the same vectors of every row (vector i of the row's 2*H*16 q/k vectors: channel
+// group l = i & 15, part and head from i >> 4), so there is no index arithmetic per element.
+template <int ITER>
 __global__ void __launch_bounds__(kThreads)
 qk_norm_rope_kernel(uint4* __restrict__ qkv, const uint4* __restrict__ qw,
                     const uint4* __restrict__ kw, const float4* __restrict__ cos_tab,
                     const float4* __restrict__ sin_tab, int64_t S, int H, float eps) {
-  const int64_t total = S * 2 * H * 16;
-  for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; (t & ~(int64_t)31) < total;
-       t += (int64_t)gridDim.x * kThreads) {
-    const bool live = t < total;
-    const int64_t tt = live ? t : total - 1;
-    const int l = (int)(tt & 15);
-    const int64_t hv = tt >> 4;
-    const int h = (int)(hv % H);
-    const int part = (int)((hv / H) & 1);
-    const int64_t s = hv / (2 * H);
-    uint4* p = qkv + ((s * 3 + part) * H + h) * 16 + l;
-    const uint4 v = *p;
-    const uint4 wv = (part == 0 ? qw : kw)[l];
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
-    float e[8];
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      e[2 * j] = bf16lo_to_f32(w[j]);
-      e[2 * j + 1] = bf16hi_to_f32(w[j]);
-      ss += e[2 * j] * e[2 * j] + e[2 * j + 1] * e[2 * j + 1];
-    }
-#pragma unroll
-    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-    const float rms = rsqrtf(ss * (1.0f / 128.0f) + eps);
+  const int vec_qk = 2 * H * 16;            // q and k are adjacent in a row
+  const int64_t row_vec = 3 * (int64_t)H * 16;
+  const int l = threadIdx.x & 15;
+  const uint32_t group_mask = 0xffffu << (threadIdx.x & 16);
+  const uint4 wq = qw[l], wk = kw[l];
+  for (int64_t s = blockIdx.x; s < S; s += gridDim.x) {
+    uint4* row = qkv + s * row_vec;
     const float4 c = cos_tab[s * 16 + l], sn = sin_tab[s * 16 + l];
-    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-    uint32_t o[4];
+    uint4 v[ITER];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float y0 = e[2 * j] * rms * bf16lo_to_f32(ww[j]);
-      const float y1 = e[2 * j + 1] * rms * bf16hi_to_f32(ww[j]);
-      o[j] = pack_bf16x2_rn(y0 * cc[j] - y1 * sv[j], y1 * cc[j] + y0 * sv[j]);
+    for (int it = 0; it < ITER; ++it) {
+      const int i = threadIdx.x + it * kThreads;
+      // a 16-lane group is live or dead as a whole (vec_qk is a multiple of 16)
+      if (i < vec_qk) v[it] = row[i];
     }
-    if (live) *p = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int i = threadIdx.x + it * kThreads;
+      if (i < vec_qk) row[i] = norm_rope_vec8(v[it], (i >> 4) >= H ? wk : wq, c, sn, eps, group_mask);
+    }
   }
 }
 
 // The same normalisation and rotation, written straight into the send buffer of the
 // sequence-parallel all-to-all instead of in place: qkv bf16 [L,3,H,128] -> send
 // [chunks][world][L][c][3][128] with head h = (p*chunks + ch)*c + ci (rank p receives its
-// heads of every chunk), V copied unchanged.  16 threads per (row, part in {q,k,v}, head).
+// heads of every chunk), V copied unchanged.  A thread keeps the same vectors of every row, so
+// the destination arithmetic runs once per thread, outside the row loop.
+template <int ITER>
 __global__ void __launch_bounds__(kThreads)
 qk_norm_rope_pack_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ send,
                          const uint4* __restrict__ qw, const uint4* __restrict__ kw,
                          const float4* __restrict__ cos_tab, const float4* __restrict__ sin_tab,
                          int64_t L, int H, int world, int chunks, float eps) {
-  const int64_t total = L * 3 * H * 16;
+  const int row_vec = 3 * H * 16;
   const int c_heads = H / (world * chunks);
-  for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; (t & ~(int64_t)31) < total;
-       t += (int64_t)gridDim.x * kThreads) {
-    const bool live = t < total;
-    const int64_t tt = live ? t : total - 1;
-    const int l = (int)(tt & 15);
-    const int64_t hv = tt >> 4;
-    const int h = (int)(hv % H);
-    const int part = (int)((hv / H) % 3);
-    const int64_t s = hv / (3 * H);
-    const uint4 v = ldg_stream(qkv + ((s * 3 + part) * H + h) * 16 + l);
-    const int seg = h / c_heads, ci = h - seg * c_heads;     // seg = p*chunks + ch
-    const int p = seg / chunks, ch = seg - p * chunks;
-    uint4* dst = send + (((((int64_t)ch * world + p) * L + s) * c_heads + ci) * 3 + part) * 16 + l;
-    // V is a plain copy.  The 16 threads of a (row, part, head) group agree on `part`, and the
-    // shuffles below stay inside such a group and name only its 16 lanes, so a V group can
-    // leave while the other half of the warp (a Q or K group when H is odd) carries on.
-    const uint32_t group_mask = 0xffffu << (threadIdx.x & 16);
-    if (part == 2) {
-      if (live) *dst = v;
-      continue;
-    }
-    const uint4 wv = (part == 1 ? kw : qw)[l];
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
-    float e[8];
-    float ss = 0.f;
+  const int l = threadIdx.x & 15;
+  const uint32_t group_mask = 0xffffu << (threadIdx.x & 16);
+  const uint4 wq = qw[l], wk = kw[l];
+  // destination of vector i of row 0, and the distance between rows there
+  int64_t dst0[ITER];
+  int part_of[ITER];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      e[2 * j] = bf16lo_to_f32(w[j]);
-      e[2 * j + 1] = bf16hi_to_f32(w[j]);
-      ss += e[2 * j] * e[2 * j] + e[2 * j + 1] * e[2 * j + 1];
+  for (int it = 0; it < ITER; ++it) {
+    const int i = threadIdx.x + it * kThreads;
+    dst0[it] = 0;
+    part_of[it] = 3;   // dead
+    if (i < row_vec) {
+      const int hp = i >> 4, part = hp / H, h = hp - part * H;
+      const int seg = h / c_heads, ci = h - seg * c_heads;     // seg = p*chunks + ch
+      const int p = seg / chunks, ch = seg - p * chunks;
+      dst0[it] = (((((int64_t)ch * world + p) * L) * c_heads + ci) * 3 + part) * 16 + l;
+      part_of[it] = part;
     }
-#pragma unroll
-    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(group_mask, ss, off);
-    const float rms = rsqrtf(ss * (1.0f / 128.0f) + eps);
+  }
+  const int64_t dst_row = (int64_t)c_heads * 3 * 16;
+  for (int64_t s = blockIdx.x; s < L; s += gridDim.x) {
+    const uint4* row = qkv + s * row_vec;
     const float4 c = cos_tab[s * 16 + l], sn = sin_tab[s * 16 + l];
-    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-    uint32_t o[4];
+    uint4 v[ITER];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float y0 = e[2 * j] * rms * bf16lo_to_f32(ww[j]);
-      const float y1 = e[2 * j + 1] * rms * bf16hi_to_f32(ww[j]);
-      o[j] = pack_bf16x2_rn(y0 * cc[j] - y1 * sv[j], y1 * cc[j] + y0 * sv[j]);
+    for (int it = 0; it < ITER; ++it)
+      if (part_of[it] < 3) v[it] = ldg_stream(row + threadIdx.x + it * kThreads);
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      if (part_of[it] == 3) continue;
+      // V is a plain copy.  The 16 lanes of a (part, head) group agree on `part`, and the
+      // shuffles stay inside the group and name only its lanes.
+      const uint4 o = part_of[it] == 2 ? v[it]
+                                       : norm_rope_vec8(v[it], part_of[it] == 1 ? wk : wq, c, sn, eps, group_mask);
+      send[dst0[it] + s * dst_row] = o;
     }
-    if (live) *dst = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -314,26 +309,44 @@ int launch_layernorm_mod(const void* x, const void* scale, const void* shift, vo
 
 int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* cos_tab,
                         const float* sin_tab, int64_t S, int H, float eps, cudaStream_t stream) {
-  const int64_t total = S * 2 * H * 16;
-  int64_t blocks = (total + kThreads - 1) / kThreads;
-  const int64_t cap = (int64_t)kNumSMsB200 * 32;
-  if (blocks > cap) blocks = cap;
-  qk_norm_rope_kernel<<<(int)blocks, kThreads, 0, stream>>>(
-      (uint4*)qkv, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab,
-      (const float4*)sin_tab, S, H, eps);
+  if (3 * H * 16 > kRopeMaxIter * kThreads)
+    return fail(B2_NOT_WHITELISTED, "qk_norm_rope: at most %d heads", kRopeMaxIter * kThreads / 48);
+  const int64_t cap = (int64_t)kNumSMsB200 * 8;
+  const int64_t blocks = S < cap ? S : cap;
+#define B2_ROPE(ITER)                                                              \
+  qk_norm_rope_kernel<ITER><<<(int)blocks, kThreads, 0, stream>>>(                 \
+      (uint4*)qkv, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab,     \
+      (const float4*)sin_tab, S, H, eps)
+  switch ((2 * H * 16 + kThreads - 1) / kThreads) {   // vectors of one row per thread
+    case 1: B2_ROPE(1); break;
+    case 2: B2_ROPE(2); break;
+    case 3: B2_ROPE(3); break;
+    default: B2_ROPE(4); break;
+  }
+#undef B2_ROPE
   return check_launch("qk_norm_rope");
 }
 
 int launch_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const void* kw,
                              const float* cos_tab, const float* sin_tab, int64_t L, int H, int world,
                              int chunks, float eps, cudaStream_t stream) {
-  const int64_t total = L * 3 * H * 16;
-  int64_t blocks = (total + kThreads - 1) / kThreads;
-  const int64_t cap = (int64_t)kNumSMsB200 * 32;
-  if (blocks > cap) blocks = cap;
-  qk_norm_rope_pack_kernel<<<(int)blocks, kThreads, 0, stream>>>(
-      (const uint4*)qkv, (uint4*)send, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab,
-      (const float4*)sin_tab, L, H, world, chunks, eps);
+  if (3 * H * 16 > kRopeMaxIter * kThreads)
+    return fail(B2_NOT_WHITELISTED, "qk_norm_rope_pack: at most %d heads", kRopeMaxIter * kThreads / 48);
+  const int64_t cap = (int64_t)kNumSMsB200 * 8;
+  const int64_t blocks = L < cap ? L : cap;
+#define B2_ROPE_PACK(ITER)                                                                       \
+  qk_norm_rope_pack_kernel<ITER><<<(int)blocks, kThreads, 0, stream>>>(                          \
+      (const uint4*)qkv, (uint4*)send, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab, \
+      (const float4*)sin_tab, L, H, world, chunks, eps)
+  switch ((3 * H * 16 + kThreads - 1) / kThreads) {   // vectors of one row per thread
+    case 1: B2_ROPE_PACK(1); break;
+    case 2: B2_ROPE_PACK(2); break;
+    case 3: B2_ROPE_PACK(3); break;
+    case 4: B2_ROPE_PACK(4); break;
+    case 5: B2_ROPE_PACK(5); break;
+    default: B2_ROPE_PACK(6); break;
+  }
+#undef B2_ROPE_PACK
   return check_launch("qk_norm_rope_pack");
 }
 

@@ -82,10 +82,10 @@ quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* 
       const int c = lane + i * TPR;
       v[i] = (live && c < kvec) ? ldg_stream(x + src0[i] + row * row_step) : make_uint4(0, 0, 0, 0);
     }
-    uint32_t acc = 0;
+    uint32_t acc = v[0].x;   // the chain starts from data (see absmax_bf16x2)
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      acc = absmax_bf16x2(acc, v[i].x);
+      if (i != 0) acc = absmax_bf16x2(acc, v[i].x);
       acc = absmax_bf16x2(acc, v[i].y);
       acc = absmax_bf16x2(acc, v[i].z);
       acc = absmax_bf16x2(acc, v[i].w);
@@ -143,88 +143,94 @@ __global__ void fill_f32_kernel(float* p, int64_t n, float v) {
 __device__ __forceinline__ float silu_exact(float g) {
   return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
 }
-// Fast SiLU: ex2.approx and rcp.approx instead of expf and the division.  Only its
-// ROUNDING TO BF16 has to equal the exact one's.  The exponent argument g*log2(e) is
-// carried as a rounded product plus its exact residual (two FMAs on the otherwise idle FMA
-// pipe), which keeps the relative error of the fast result within a few fp32 ulps for
-// |g| <= 64; whenever the fast fp32 result lies more than 16 ulps away from a bf16 rounding
-// midpoint (low 16 bits == 0x8000) both versions therefore round to the same bf16.
-// Otherwise *sure is cleared and the caller recomputes exactly (0.05 % of the elements).
-// tests/test_gpu_int8_path.py checks the result against the eager op for all 65536 gates.
-__device__ __forceinline__ float silu_fast(float g, bool* sure) {
-  constexpr float kNegLog2eHi = -1.4426950216293335f;   // fp32(log2 e), negated
-  constexpr float kNegLog2eLo = -1.9259629911266175e-8f;  // log2 e - fp32(log2 e), negated
-  const float t = g * kNegLog2eHi;
-  float r = fmaf(g, kNegLog2eHi, -t);  // exact rounding residual of the product
-  r = fmaf(g, kNegLog2eLo, r);
-  float e, rc;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
-  e = fmaf(e, r * 0.6931471805599453f, e);  // 2^(t+r) = 2^t * (1 + r ln 2)
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + e));
-  const float s = g * rc;
-  // |g| <= 64 keeps every intermediate finite and normal (beyond it: exact path)
-  *sure = (fabsf(g) <= 64.0f) && (((__float_as_uint(s) & 0xffffu) - (0x8000u - 16u)) > 32u);
-  return s;
+
+// bf16(silu(g)) depends on the 16 bits of the bf16 gate alone, so the whole function is a
+// table of 65536 bf16 values (128 KB).  It is built once per device from the exact formula
+// above and every CTA of the row kernel keeps a copy in shared memory: the first rounding of
+// the operator then costs one shared-memory load per element instead of two trips through
+// the transcendental unit (exp2, reciprocal) plus the bookkeeping that made their result
+// bit-exact, and it is exact by construction for every gate, NaN and infinities included.
+constexpr int kSiluEntries = 65536;
+__device__ __align__(16) uint16_t g_silu_bf16[kSiluEntries];
+
+__global__ void build_silu_table_kernel() {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < (uint32_t)kSiluEntries)
+    g_silu_bf16[i] = __bfloat16_as_ushort(__float2bfloat16_rn(silu_exact(__uint_as_float(i << 16))));
 }
 
-// bf16( bf16(silu(g)) * u ) on a packed pair; two bf16 roundings.
-__device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
-  const float g0 = bf16lo_to_f32(g), g1 = bf16hi_to_f32(g);
-  bool sure0, sure1;
-  float s0 = silu_fast(g0, &sure0);
-  float s1 = silu_fast(g1, &sure1);
-  // A vote over the lanes that are converged here keeps the rare exact path a real branch
-  // instead of predicated code.  The mask must be the ACTIVE mask: the scalar fallback
-  // kernel calls this from loops whose trip count differs between lanes.
-  if (__any_sync(__activemask(), !(sure0 && sure1))) {
-    s0 = silu_exact(g0);
-    s1 = silu_exact(g1);
-  }
+// bf16( bf16(silu(g)) * u ) on a packed pair from the exact formula (generic kernel).
+__device__ __forceinline__ uint32_t swiglu_pair_exact(uint32_t g, uint32_t u) {
+  const uint32_t s = pack_bf16x2_rn(silu_exact(bf16lo_to_f32(g)), silu_exact(bf16hi_to_f32(g)));
   // second rounding: the fp32 product of two bf16 values is exact, so rounding it to bf16 is
-  // the packed bf16 multiply's single rounding (one FMA-pipe instruction instead of seven)
-  return bf16x2_mul_rn(pack_bf16x2_rn(s0, s1), u);
+  // the packed bf16 multiply's single rounding
+  return bf16x2_mul_rn(s, u);
 }
+// The same through the table in shared memory.
+__device__ __forceinline__ uint32_t swiglu_pair_lut(uint32_t g, uint32_t u, const uint16_t* lut) {
+  const uint32_t s = (uint32_t)lut[g & 0xffffu] | ((uint32_t)lut[g >> 16] << 16);
+  return bf16x2_mul_rn(s, u);
+}
+
+constexpr int kSwigluThreads = 512;
+constexpr int kSwigluSmem = kSiluEntries * 2;   // dynamic shared memory: the table
 
 template <int TPR, int VPT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kSwigluThreads, 1)
 swiglu_quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
                             float* __restrict__ scales, int64_t M, int kvec) {
-  __shared__ float red[kThreads / 32];
-  constexpr int RPC = kThreads / TPR;
+  extern __shared__ __align__(16) uint16_t lut[];
+  __shared__ float red[3][kSwigluThreads / 32];   // three reduction buffers in rotation (slot_allreduce)
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(g_silu_bf16);
+    uint4* dst = reinterpret_cast<uint4*>(lut);
+    for (int i = threadIdx.x; i < kSwigluSmem / 16; i += kSwigluThreads) dst[i] = src[i];
+  }
+  __syncthreads();
+  constexpr int RPC = kSwigluThreads / TPR;
   const int slot = threadIdx.x / TPR;
   const int lane = threadIdx.x % TPR;
-  for (int64_t row0 = (int64_t)blockIdx.x * RPC; row0 < M; row0 += (int64_t)gridDim.x * RPC) {
-    const int64_t row = row0 + slot;
+  // The next row's vectors are requested before the current row is processed, so the loads
+  // of one row overlap the arithmetic and the stores of the previous one.
+  auto load_row = [&](int64_t row, uint4 (&g)[VPT], uint4 (&u)[VPT]) {
     const bool live = row < M;
     const uint4* gr = x + row * (2 * (int64_t)kvec);  // gate half
     const uint4* ur = gr + kvec;                       // up half
-    uint4 a[VPT];
-    {
-      uint4 g[VPT], u[VPT];
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int c = lane + i * TPR;
-        const bool ok = live && c < kvec;
-        g[i] = ok ? ldg_stream(gr + c) : make_uint4(0, 0, 0, 0);
-        u[i] = ok ? ldg_stream(ur + c) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        a[i].x = swiglu_pair(g[i].x, u[i].x);
-        a[i].y = swiglu_pair(g[i].y, u[i].y);
-        a[i].z = swiglu_pair(g[i].z, u[i].z);
-        a[i].w = swiglu_pair(g[i].w, u[i].w);
-      }
-    }
-    uint32_t acc = 0;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      acc = absmax_bf16x2(acc, a[i].x);
+      const int c = lane + i * TPR;
+      const bool ok = live && c < kvec;
+      g[i] = ok ? ldg_stream(gr + c) : make_uint4(0, 0, 0, 0);
+      u[i] = ok ? ldg_stream(ur + c) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  const int64_t stride = (int64_t)gridDim.x * RPC;
+  uint4 g[VPT], u[VPT];
+  load_row((int64_t)blockIdx.x * RPC + slot, g, u);
+  int phase = 0;
+  for (int64_t row0 = (int64_t)blockIdx.x * RPC; row0 < M; row0 += stride) {
+    const int64_t row = row0 + slot;
+    const bool live = row < M;
+    uint4 gn[VPT], un[VPT];
+    load_row(row + stride, gn, un);
+    uint4 a[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      a[i].x = swiglu_pair_lut(g[i].x, u[i].x, lut);
+      a[i].y = swiglu_pair_lut(g[i].y, u[i].y, lut);
+      a[i].z = swiglu_pair_lut(g[i].z, u[i].z, lut);
+      a[i].w = swiglu_pair_lut(g[i].w, u[i].w, lut);
+    }
+    uint32_t acc = a[0].x;   // the chain starts from data (see absmax_bf16x2)
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (i != 0) acc = absmax_bf16x2(acc, a[i].x);
       acc = absmax_bf16x2(acc, a[i].y);
       acc = absmax_bf16x2(acc, a[i].z);
       acc = absmax_bf16x2(acc, a[i].w);
     }
-    const float absmax = row_allreduce_max<TPR>(fold_absmax(acc), red);
+    const float absmax = slot_allreduce<kSwigluThreads, TPR>(fold_absmax(acc), red[phase], slot, NanMaxOp());
+    phase = phase == 2 ? 0 : phase + 1;
     float r;
     bool zero_row;
     const float scale = row_scale_from_absmax(absmax, &r, &zero_row);
@@ -237,7 +243,11 @@ swiglu_quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
         if (c < kvec) qr[c] = zero_row ? make_uint2(0, 0) : quant_vec8(a[i], r);
       }
     }
-    if constexpr (TPR > 32) __syncthreads();
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      g[i] = gn[i];
+      u[i] = un[i];
+    }
   }
 }
 
@@ -251,7 +261,7 @@ swiglu_quantize_rows_generic_kernel(const __nv_bfloat16* __restrict__ x, int8_t*
     const __nv_bfloat16* ur = gr + K;
     float m = 0.0f;
     for (int64_t c = threadIdx.x; c < K; c += kThreads) {
-      const uint32_t a = swiglu_pair(__bfloat16_as_ushort(gr[c]), __bfloat16_as_ushort(ur[c]));
+      const uint32_t a = swiglu_pair_exact(__bfloat16_as_ushort(gr[c]), __bfloat16_as_ushort(ur[c]));
       m = nanmax(m, fabsf(bf16lo_to_f32(a)));
     }
     const float absmax = row_allreduce_max<kThreads>(m, red);
@@ -260,7 +270,7 @@ swiglu_quantize_rows_generic_kernel(const __nv_bfloat16* __restrict__ x, int8_t*
     const float scale = row_scale_from_absmax(absmax, &r, &zero_row);
     if (threadIdx.x == 0) scales[row] = scale;
     for (int64_t c = threadIdx.x; c < K; c += kThreads) {
-      const uint32_t a = swiglu_pair(__bfloat16_as_ushort(gr[c]), __bfloat16_as_ushort(ur[c]));
+      const uint32_t a = swiglu_pair_exact(__bfloat16_as_ushort(gr[c]), __bfloat16_as_ushort(ur[c]));
       q[row * K + c] = zero_row ? (int8_t)0 : (int8_t)(quant_pair(a & 0xffffu, r) & 0xffu);
     }
     __syncthreads();
@@ -309,23 +319,64 @@ int launch_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K
   return launch_quantize_gathered(x, q, scale, M, K, 0, 1, stream);
 }
 
+namespace {
+
+// Once per device: build the SiLU table (and wait for it, so that a first call from another
+// stream of the same device cannot run ahead of it).  The wait makes the very first call on a
+// device unsuitable for a stream capture; every later call only enqueues.
+int ensure_silu_table(cudaStream_t stream) {
+  static PerDeviceSetup per_device;
+  const DeviceSlot* slot = nullptr;
+  return per_device.get("swiglu_quantize_int8_rowwise", [stream](int, DeviceSlot&) -> int {
+    build_silu_table_kernel<<<kSiluEntries / 256, 256, 0, stream>>>();
+    int st = check_launch("swiglu_quantize_int8_rowwise (table)");
+    if (st != B2_OK) return st;
+    const cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess)
+      return fail(B2_LAUNCH_FAILED, "swiglu_quantize_int8_rowwise: building the SiLU table: %s (the first "
+                  "call on a device must come before any stream capture)", cudaGetErrorString(e));
+    return B2_OK;
+  }, &slot);
+}
+
+template <int TPR, int VPT>
+int launch_swiglu_rows(const void* x, int8_t* q, float* scale, int64_t M, int kvec, cudaStream_t stream) {
+  static PerDeviceSetup per_device;   // one per instantiation: the shared-memory opt-in is per kernel and device
+  const DeviceSlot* slot = nullptr;
+  const int st = per_device.get("swiglu_quantize_int8_rowwise", [](int dev, DeviceSlot& s) -> int {
+    const cudaError_t e = cudaFuncSetAttribute(swiglu_quantize_rows_kernel<TPR, VPT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSwigluSmem);
+    if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "swiglu_quantize_int8_rowwise: smem attribute: %s", cudaGetErrorString(e));
+    s.a = kNumSMsB200;
+    cudaDeviceGetAttribute(&s.a, cudaDevAttrMultiProcessorCount, dev);
+    return B2_OK;
+  }, &slot);
+  if (st != B2_OK) return st;
+  constexpr int RPC = kSwigluThreads / TPR;
+  const int64_t need = (M + RPC - 1) / RPC;
+  const int grid = (int)(need < slot->a ? need : slot->a);   // one CTA per SM (its table fills the shared memory)
+  swiglu_quantize_rows_kernel<TPR, VPT><<<grid, kSwigluThreads, kSwigluSmem, stream>>>(
+      (const uint4*)x, (uint2*)q, scale, M, kvec);
+  return check_launch("swiglu_quantize_int8_rowwise");
+}
+
+}  // namespace
+
 int launch_swiglu_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                            cudaStream_t stream) {
   const bool vec_ok = (K % 8 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
   const int kvec = (int)(K / 8);
-#define B2_S(TPR, VPT)                                                                   \
-  swiglu_quantize_rows_kernel<TPR, VPT>                                                  \
-      <<<grid_for_rows(M, kThreads / TPR, 8), kThreads, 0, stream>>>((const uint4*)x, (uint2*)q, \
-                                                                     scale, M, kvec)
-  if (vec_ok && K <= 1024) B2_S(32, 4);
-  else if (vec_ok && K <= 2048) B2_S(64, 4);
-  else if (vec_ok && K <= 4096) B2_S(128, 4);
-  else if (vec_ok && K <= 8192) B2_S(256, 4);
-  else if (vec_ok && K <= 16384) B2_S(256, 8);
-  else
-    swiglu_quantize_rows_generic_kernel<<<grid_for_rows(M, 1, 8), kThreads, 0, stream>>>(
-        (const __nv_bfloat16*)x, q, scale, M, K);
-#undef B2_S
+  if (vec_ok && K <= 16384) {
+    const int st = ensure_silu_table(stream);
+    if (st != B2_OK) return st;
+    if (K <= 1024) return launch_swiglu_rows<32, 4>(x, q, scale, M, kvec, stream);
+    if (K <= 2048) return launch_swiglu_rows<64, 4>(x, q, scale, M, kvec, stream);
+    if (K <= 4096) return launch_swiglu_rows<128, 4>(x, q, scale, M, kvec, stream);
+    if (K <= 8192) return launch_swiglu_rows<256, 4>(x, q, scale, M, kvec, stream);
+    return launch_swiglu_rows<512, 4>(x, q, scale, M, kvec, stream);
+  }
+  swiglu_quantize_rows_generic_kernel<<<grid_for_rows(M, 1, 8), kThreads, 0, stream>>>(
+      (const __nv_bfloat16*)x, q, scale, M, K);
   return check_launch("swiglu_quantize_int8_rowwise");
 }
 
