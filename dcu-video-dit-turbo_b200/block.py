@@ -145,8 +145,12 @@ class GraphedBlock:
     host-side launch gaps between them.  Shapes, weights and the rotary tables are
     fixed at capture time; `__call__` copies the input into the captured buffer, replays
     and returns the captured output buffer (overwritten by the next call).
-    Warm-up passes run first so that one-time host work (function attributes, library
-    loading) never happens inside the capture."""
+    Warm-up passes run first so that one-time host work (function attributes, lookup
+    tables, library loading) never happens inside the capture.
+    The sequence-parallel pass stays eager: a capture that included its all-to-all
+    collectives on the side stream did not come back within five minutes on two GPUs (at
+    23638 and at 5910 tokens), and at the per-GPU kernel sizes of that pass the host enqueues
+    faster than the GPU runs anyway."""
 
     def __init__(self, block: DiTBlock, x_example: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                  warmup: int = 3):
