@@ -590,9 +590,14 @@ def run_b200(args):
     ops.check_device_status(dev)
 
     pk = peaks()
+    # per-kernel table: every rank runs the passes (they contain collectives), rank 0 reports.
+    # At N > 1 the rows are this rank's kernels; what the step takes beyond their sum is the
+    # exposed part of the all-to-alls plus launch gaps.
     kernels = None
-    if world == 1 and not args.no_kernels:
-        kernels = kernel_table(pkg, blk, x_dev, cos, sin, pk) + standalone_rows(pkg, T, dev, pk)
+    if not args.no_kernels:
+        kernels = kernel_table(pkg, blk, x_dev, cos, sin, pk)
+        if world == 1:
+            kernels += standalone_rows(pkg, T, dev, pk)
 
     # ---- the second token count of the metric (23638), same ranks, same protocol ----
     small = None
@@ -618,8 +623,10 @@ def run_b200(args):
                  "parallelism": (f"ulysses_sp{world}_headchunks{job2.chunks}" if world > 1 else
                                  ("single_gpu_cuda_graph" if not args.no_graph else "single_gpu"))}
         if kernels is not None:
-            small["kernels"] = kernel_table(pkg, job2.block, x2, job2.cos, job2.sin, pk, passes=5) + \
-                standalone_rows(pkg, SMALL_TOKENS, dev, pk)
+            small["kernels"] = kernel_table(pkg, job2.block, x2, job2.cos, job2.sin, pk, passes=5)
+            small["kernels_ms_sum"] = sum(k["ms"] for k in small["kernels"])
+            if world == 1:
+                small["kernels"] += standalone_rows(pkg, SMALL_TOKENS, dev, pk)
         ops.check_device_status(dev)
 
     if rank != 0:
@@ -674,6 +681,7 @@ def run_b200(args):
         line["block_23638"] = small
     if kernels is not None:
         line["kernels"] = kernels
+        line["kernels_ms_sum"] = sum(k["ms"] for k in kernels if "standalone" not in k["kernel"])
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_block_ms(T, args.cpu_seconds)
     print(json.dumps(line))

@@ -66,7 +66,8 @@ const char* b2_status_string(int s) {
 int b2_check_device_status(void* stream) {
   cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
   if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "stream synchronize: %s", cudaGetErrorString(e));
-  const unsigned int word = read_clear_status_gemm() | read_clear_status_gemm2() | read_clear_status_flash();
+  const unsigned int word = read_clear_status_gemm() | read_clear_status_gemm2() | read_clear_status_flash() |
+                            read_clear_status_flash2();
   if (word == 0xffffffffu) return fail(B2_LAUNCH_FAILED, "status word could not be read");
   if (word != 0) return fail(B2_TIMEOUT, "device-side bounded wait gave up (code 0x%x)", word);
   return B2_OK;

@@ -44,10 +44,16 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* out, int
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
                      cudaStream_t stream);
 
+// CTA-pair (cta_group::2) variant; returns -1 when it does not apply.
+int launch_flash_fwd_pair(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
+                          const int64_t* qs, const int64_t* ks, const int64_t* vs, float scale,
+                          cudaStream_t stream);
+
 int launch_bounded_wait_selftest(cudaStream_t stream);
 // Read and clear the device-side status word of a tensor-core translation unit.
 unsigned int read_clear_status_gemm();
 unsigned int read_clear_status_gemm2();
 unsigned int read_clear_status_flash();
+unsigned int read_clear_status_flash2();
 
 }  // namespace b2

@@ -193,3 +193,34 @@ def test_bounded_wait_reports_timeout_and_context_survives(cuda_pkg):
     out = cuda_pkg.ops.fwd_bhsd(q, q, q, 128 ** -0.5)
     assert torch.isfinite(out.float()).all()
     cuda_pkg.ops.check_device_status()
+
+
+def test_cta_pair_variant_gives_the_same_bits(cuda_pkg, tmp_path):
+    """The opt-in CTA-pair kernel (B2_FLASH_PAIR=1, read once per process) against the default
+    kernel: same softmax arithmetic, same MMA order per row, so the outputs are bitwise equal,
+    ragged tails, a second CTA without valid rows and a strided layout included."""
+    import os
+    import subprocess
+    import sys
+    cases = [(300, "chunk"), (129, "standard"), (1024, "standard"), (777, "qkv"), (2500, "standard")]
+    want = {}
+    for seq, layout in cases:
+        q, k, v = make_qkv(seq, 3, 7 + seq, layout)
+        want[seq] = cuda_pkg.ops.fwd_bhsd(to_dev(q), to_dev(k), to_dev(v), 128 ** -0.5).cpu()
+        torch.save(want[seq], tmp_path / f"want_{seq}.pt")
+    script = f"""
+import sys, importlib, torch
+sys.path.insert(0, {str(Path(__file__).resolve().parents[1])!r})
+sys.path.insert(0, {str(Path(__file__).resolve().parent)!r})
+import test_gpu_flash as T
+pkg = importlib.import_module("dcu-video-dit-turbo_b200")
+for seq, layout in {cases!r}:
+    q, k, v = T.make_qkv(seq, 3, 7 + seq, layout)
+    got = pkg.ops.fwd_bhsd(T.to_dev(q), T.to_dev(k), T.to_dev(v), 128 ** -0.5).cpu()
+    pkg.ops.check_device_status()
+    assert torch.equal(got, torch.load({str(tmp_path)!r} + f"/want_{{seq}}.pt")), seq
+print("pair ok")
+"""
+    env = dict(os.environ, B2_FLASH_PAIR="1")
+    out = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "pair ok" in out.stdout, out.stdout + out.stderr
