@@ -395,9 +395,10 @@ def kernel_table(pkg, block, x, cos, sin, pk, passes=3):
     recs = timer.results()
     per = len(recs) // passes
     labels = ["layernorm_mod_quant (adaLN 1)", "int8_gemm_dequant qkv 3072->9216", "qk_norm_rope",
-              "flash_fwd", "quantize_int8_rowwise (attention rows)", "int8_gemm_dequant out 3072->3072",
-              "gate_residual", "layernorm_mod_quant (adaLN 2)", "int8_gemm_dequant fc1 3072->16384",
-              "swiglu_quantize_int8_rowwise", "int8_gemm_dequant_residual fc2 8192->3072"]
+              "flash_fwd", "quantize_int8_rowwise (attention rows)",
+              "int8_gemm_dequant_residual out 3072->3072", "layernorm_mod_quant (adaLN 2)",
+              "int8_gemm_dequant fc1 3072->16384", "swiglu_quantize_int8_rowwise",
+              "int8_gemm_dequant_residual fc2 8192->3072"]
     rows = []
     for i in range(per):
         ms = statistics.median(recs[p * per + i]["ms"] for p in range(passes))
@@ -503,7 +504,7 @@ def run_b200(args):
         y = blk.forward(x_dev, cos, sin)
     ops.check_device_status(dev)
     attn_events.clear()
-    # single GPU: the pass is replayed from a CUDA graph (one launch instead of eleven); the
+    # single GPU: the pass is replayed from a CUDA graph (one launch instead of ten); the
     # attention events are then recorded by a second, eager run of the same steps
     use_graph = world == 1 and not args.no_graph
     run_step = lambda: blk.forward(x_dev, cos, sin)

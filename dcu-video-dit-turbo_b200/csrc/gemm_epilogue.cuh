@@ -60,8 +60,63 @@ __device__ __forceinline__ void epilogue_prefetch_residual(const EpilogueArgs& a
     if (col0 + b / 2 < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + b));
 }
 
-// One 32-column chunk of one row.  `c` is the chunk's offset inside the tile, `col` its
-// global column; the row is valid and col < N (checked by the caller).
+// Dequant (+ bias, + gated residual) of one 32-column chunk of one row into 16 packed bf16
+// words.  `c` is the chunk's offset inside the tile, `col` its global column (< N).  In
+// residual mode x is read here (8 columns per 16-byte load); 8-column groups at or beyond N are
+// left as zeros (they are never stored).
+__device__ __forceinline__ void epilogue_compute_chunk(const EpilogueArgs& a, const uint32_t (&v)[32],
+                                                       int row, int col, int c, float rsv,
+                                                       const float* cvec, uint32_t (&o)[16]) {
+  const float* cscale = cvec + c;
+  const float* cbias = cvec + kEpiTileN + c;
+  const float* cgate = cvec + 2 * kEpiTileN + c;
+  const bool has_bias = a.bias_kind != B2_BIAS_NONE;
+  const bool residual = a.gate != nullptr;
+  const uint4* xsrc = residual ? reinterpret_cast<const uint4*>(a.residual + (int64_t)row * a.N + col) : nullptr;
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) {  // N % 8 == 0: whole 8-column groups are in or out
+    uint4 xv = make_uint4(0, 0, 0, 0);
+    const bool in = col + j4 * 8 < a.N;
+    if (residual && in && row < a.M) xv = xsrc[j4];
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int j = j4 * 4 + jj;
+      const float f0 = __fmul_rn(__int2float_rn((int)v[2 * j]), __fmul_rn(rsv, cscale[2 * j]));
+      const float f1 = __fmul_rn(__int2float_rn((int)v[2 * j + 1]), __fmul_rn(rsv, cscale[2 * j + 1]));
+      uint32_t p = pack_bf16x2_rn(f0, f1);
+      if (has_bias)
+        p = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(p), cbias[2 * j]),
+                           __fadd_rn(bf16hi_to_f32(p), cbias[2 * j + 1]));
+      if (residual) {
+        const uint32_t g = pack_bf16x2_rn(__fmul_rn(bf16lo_to_f32(p), cgate[2 * j]),
+                                          __fmul_rn(bf16hi_to_f32(p), cgate[2 * j + 1]));
+        p = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(xw[jj]), bf16lo_to_f32(g)),
+                           __fadd_rn(bf16hi_to_f32(xw[jj]), bf16hi_to_f32(g)));
+      }
+      o[j] = in ? p : 0u;
+    }
+  }
+}
+
+// Staging tile of one epilogue warp for the TMA-store path: 32 rows (one per lane) x 64 bf16
+// columns = 32 x 128 bytes in the 128-byte-swizzle layout of a tensor-map box {64, 32}: the
+// 16-byte chunk k of row r sits at r*128 + ((k ^ (r & 7)) * 16).  1024-byte aligned.
+constexpr int kEpiStageBytes = 32 * 128;
+// Lane `lane` writes its 16 packed words of 32-column half `half` (0 or 1) of the 64-column step.
+__device__ __forceinline__ void epilogue_stage_write(uint32_t stage_smem, int lane, int half,
+                                                     const uint32_t (&o)[16]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t addr = stage_smem + lane * 128 + (((half * 4 + k) ^ (lane & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[4 * k]), "r"(o[4 * k + 1]),
+                 "r"(o[4 * k + 2]), "r"(o[4 * k + 3])
+                 : "memory");
+  }
+}
+
+// One 32-column chunk of one row, stored directly.  `c` is the chunk's offset inside the tile,
+// `col` its global column; the row is valid and col < N (checked by the caller).
 __device__ __forceinline__ void epilogue_store_chunk(const EpilogueArgs& a, const uint32_t (&v)[32],
                                                      int row, int col, int c, float rsv,
                                                      const float* cvec) {

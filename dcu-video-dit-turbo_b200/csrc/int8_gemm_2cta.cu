@@ -15,8 +15,11 @@
 //           shared memory, completes bytes on the LEADER's `full` barrier
 //   warp 1  MMA issuer (leader only): 256x256x32 MMAs; tcgen05.commit multicasts to both
 //           CTAs' `empty` / `tmem_full` barriers
-//   warps 2-5 epilogue (both CTAs): own accumulator rows -> scales, bias, bf16 -> global;
-//           arrive on the leader's `tmem_empty` barrier (remote arrive for the peer)
+//   warps 2-5 epilogue (both CTAs): own accumulator rows -> scales, bias, bf16; each warp stages
+//           32 rows x 64 columns in shared memory (128-byte swizzle) and ONE lane hands the
+//           tile to a TMA store, so the output leaves as whole 128-byte lines instead of 32
+//           separate 16-byte pieces per instruction, and ragged edges are clipped by the
+//           tensor map; arrive on the leader's `tmem_empty` barrier (remote for the peer)
 // All mbarrier waits are bounded; both CTAs always meet at a final cluster barrier before
 // either frees tensor memory or exits, so no CTA touches a retired peer.
 #include <cstdlib>
@@ -47,9 +50,11 @@ constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;       // 256-row tiles swept per N pass
 
 constexpr int SMEM_RING = STAGES * STAGE_BYTES;
+constexpr int SMEM_OUT = (EPI_THREADS / 32) * kEpiStageBytes;  // one staging tile per epilogue warp
 constexpr int SMEM_COLVEC = 2 * kColVecFloats * 4;  // [buf][scale|bias|gate][256] fp32
 constexpr int NUM_BARS = 2 * STAGES + 4;
-constexpr int SMEM_TOTAL = 1024 + SMEM_RING + SMEM_COLVEC + NUM_BARS * 8 + 16;
+constexpr int SMEM_TOTAL = 1024 + SMEM_RING + SMEM_OUT + SMEM_COLVEC + NUM_BARS * 8 + 16;
+static_assert(SMEM_TOTAL <= 227 * 1024, "shared memory budget");
 
 struct Gemm2Args {
   int M, N, K;
@@ -120,12 +125,13 @@ __device__ __forceinline__ void mma_i8_ss_pair(uint32_t d_tmem, uint64_t adesc, 
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                      const __grid_constant__ CUtensorMap tmap_b, const Gemm2Args args) {
+                      const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_out, const Gemm2Args args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  float* colvec = reinterpret_cast<float*>(smem + SMEM_RING);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_RING + SMEM_COLVEC);
+  float* colvec = reinterpret_cast<float*>(smem + SMEM_RING + SMEM_OUT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_RING + SMEM_OUT + SMEM_COLVEC);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -152,6 +158,7 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
@@ -246,12 +253,43 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = row < epi.M;
       const float rsv = (fused && row_ok) ? epi.rs[row] : 0.f;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      if (fused) {
+        // 64 columns per step: two 32-column halves are computed into the warp's staging tile,
+        // then one lane issues the TMA store of the 32 x 64 tile
+        const uint32_t stage = ring + SMEM_RING + quarter * kEpiStageBytes;
+        const int row_warp = row - lane;   // global row of lane 0
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c, v);
-        tmem_wait_ld();
-        if (row_ok && col0 + c < epi.N) epilogue_store_chunk(epi, v, row, col0 + c, c, rsv, cvec);
+        for (int c = 0; c < BN; c += 64) {
+          if (col0 + c >= epi.N) break;
+          if (lane == 0) bulk_wait_group_read<0>();   // the previous store has read the tile
+          __syncwarp();
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t v[32];
+            uint32_t o[16];
+            tmem_ld_32x32b_x32(taddr + c + 32 * hh, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = 0u;
+            if (col0 + c + 32 * hh < epi.N)
+              epilogue_compute_chunk(epi, v, row, col0 + c + 32 * hh, c + 32 * hh, rsv, cvec, o);
+            epilogue_stage_write(stage, lane, hh, o);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row_warp < epi.M) {
+            tma_store_2d(&tmap_out, stage, col0 + c, row_warp);
+            bulk_commit_group();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c, v);
+          tmem_wait_ld();
+          if (row_ok && col0 + c < epi.N) epilogue_store_chunk(epi, v, row, col0 + c, c, rsv, cvec);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -259,6 +297,7 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       buf ^= 1;
       if (buf == 0) buf_phase ^= 1;
     }
+    if (lane == 0) bulk_wait_group<0>();   // this warp's stores are complete before the CTA may retire
   }
 
   // ------------------------------- teardown -------------------------------
@@ -288,6 +327,22 @@ int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int 
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B2_LAUNCH_FAILED, "int8_gemm: tensor map encode failed (%d)", (int)r);
+  return B2_OK;
+}
+
+// bf16 [M, N] output (or the in-place residual operand) as boxes of 64 columns x 32 rows,
+// 128-byte swizzle: what one epilogue warp stages per step.
+int encode_out_map(CUtensorMap* map, void* base, int64_t M, int64_t N) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return fail(B2_LAUNCH_FAILED, "int8_gemm: cuTensorMapEncodeTiled is unavailable");
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B2_LAUNCH_FAILED, "int8_gemm: output tensor map encode failed (%d)", (int)r);
   return B2_OK;
 }
 
@@ -338,11 +393,19 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
   const int enabled = slot->a, max_clusters = slot->b;
   if (!enabled || M < 2 * BM) return -1;
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tout;
   int st = encode_map(&ta, A, M, K, BM);
   if (st != B2_OK) return st;
   st = encode_map(&tb, W, N, K, BNH);
   if (st != B2_OK) return st;
+  // fused modes store through this map (the plain int32 mode stores directly and never uses it)
+  void* bf16_dst = residual != nullptr ? residual : out_bf16;
+  if (bf16_dst != nullptr) {
+    st = encode_out_map(&tout, bf16_dst, M, N);
+    if (st != B2_OK) return st;
+  } else {
+    tout = ta;
+  }
   Gemm2Args a;
   a.M = (int)M;
   a.N = (int)N;
@@ -364,7 +427,7 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
   a.epi.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
   a.epi.residual = reinterpret_cast<__nv_bfloat16*>(residual);
   const int clusters = a.num_tiles < max_clusters ? a.num_tiles : max_clusters;
-  int8_gemm_2cta_kernel<<<clusters * 2, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, a);
+  int8_gemm_2cta_kernel<<<clusters * 2, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, tout, a);
   return check_launch("int8_gemm (CTA pair)");
 }
 
