@@ -175,7 +175,8 @@ __device__ __forceinline__ uint32_t swiglu_pair_lut(uint32_t g, uint32_t u, cons
 constexpr int kSwigluThreads = 512;
 constexpr int kSwigluSmem = kSiluEntries * 2;   // dynamic shared memory: the table
 
-template <int TPR, int VPT>
+// FULL: the row fills every vector of every thread (K == TPR*VPT*8): no per-vector range tests.
+template <int TPR, int VPT, bool FULL>
 __global__ void __launch_bounds__(kSwigluThreads, 1)
 swiglu_quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
                             float* __restrict__ scales, int64_t M, int kvec) {
@@ -199,7 +200,7 @@ swiglu_quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + i * TPR;
-      const bool ok = live && c < kvec;
+      const bool ok = live && (FULL || c < kvec);
       g[i] = ok ? ldg_stream(gr + c) : make_uint4(0, 0, 0, 0);
       u[i] = ok ? ldg_stream(ur + c) : make_uint4(0, 0, 0, 0);
     }
@@ -240,7 +241,7 @@ swiglu_quantize_rows_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int c = lane + i * TPR;
-        if (c < kvec) qr[c] = zero_row ? make_uint2(0, 0) : quant_vec8(a[i], r);
+        if (FULL || c < kvec) qr[c] = zero_row ? make_uint2(0, 0) : quant_vec8(a[i], r);
       }
     }
 #pragma unroll
@@ -344,8 +345,11 @@ int launch_swiglu_rows(const void* x, int8_t* q, float* scale, int64_t M, int kv
   static PerDeviceSetup per_device;   // one per instantiation: the shared-memory opt-in is per kernel and device
   const DeviceSlot* slot = nullptr;
   const int st = per_device.get("swiglu_quantize_int8_rowwise", [](int dev, DeviceSlot& s) -> int {
-    const cudaError_t e = cudaFuncSetAttribute(swiglu_quantize_rows_kernel<TPR, VPT>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSwigluSmem);
+    cudaError_t e = cudaFuncSetAttribute(swiglu_quantize_rows_kernel<TPR, VPT, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSwigluSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(swiglu_quantize_rows_kernel<TPR, VPT, false>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSwigluSmem);
     if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "swiglu_quantize_int8_rowwise: smem attribute: %s", cudaGetErrorString(e));
     s.a = kNumSMsB200;
     cudaDeviceGetAttribute(&s.a, cudaDevAttrMultiProcessorCount, dev);
@@ -355,8 +359,12 @@ int launch_swiglu_rows(const void* x, int8_t* q, float* scale, int64_t M, int kv
   constexpr int RPC = kSwigluThreads / TPR;
   const int64_t need = (M + RPC - 1) / RPC;
   const int grid = (int)(need < slot->a ? need : slot->a);   // one CTA per SM (its table fills the shared memory)
-  swiglu_quantize_rows_kernel<TPR, VPT><<<grid, kSwigluThreads, kSwigluSmem, stream>>>(
-      (const uint4*)x, (uint2*)q, scale, M, kvec);
+  if (kvec == TPR * VPT)
+    swiglu_quantize_rows_kernel<TPR, VPT, true><<<grid, kSwigluThreads, kSwigluSmem, stream>>>(
+        (const uint4*)x, (uint2*)q, scale, M, kvec);
+  else
+    swiglu_quantize_rows_kernel<TPR, VPT, false><<<grid, kSwigluThreads, kSwigluSmem, stream>>>(
+        (const uint4*)x, (uint2*)q, scale, M, kvec);
   return check_launch("swiglu_quantize_int8_rowwise");
 }
 
