@@ -88,7 +88,11 @@ int b2_mod_scale_shift(void* x_bf16, const void* scale_bf16, const void* shift_b
 
 /* Fused SwiGLU + rowwise quantizer: x bf16 [M,2K] -> q int8 [M,K], scale fp32 [M].
  * Replaces h3_swiglu_quantize_int8_rowwise_hip, kernels/swiglu-quant/swiglu_quant_kernel.hip:111-137
- * (Python: swiglu_quantize_int8_rowwise(x), kernels/swiglu-quant/swiglu_quant.cpp:5-9). */
+ * (Python: swiglu_quantize_int8_rowwise(x), kernels/swiglu-quant/swiglu_quant.cpp:5-9).
+ * bf16(silu(gate)) comes from a 65536-entry table held in a fixed array inside the library
+ * (128 KB per GPU, no allocation).  The FIRST call on each device fills it with the exact
+ * formula and waits for that kernel on `stream`; make that call before any stream capture.
+ * The same holds for b2_int8_linear with B2_ACT_SWIGLU and for b2_int8_linear_noalloc. */
 int b2_swiglu_quantize_int8_rowwise(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                                     void* stream);
 
