@@ -32,7 +32,7 @@ constexpr int NUM_THREADS = (kSoftmaxWarps + 4) * 32;   // 384: two softmax warp
 // Which of the 8 score pairs of a 16-column chunk take their exponential on the FMA pipe
 // (bit i = pair i) instead of the exp2 unit.
 #ifndef B2_FLASH_EMU_MASK
-#define B2_FLASH_EMU_MASK 0x88
+#define B2_FLASH_EMU_MASK 0x22
 #endif
 // setmaxnreg.inc waits, without a limit, until the registers it asks for are free in the
 // CTA's own allocation, so the split must fit into what the kernel was launched with:
