@@ -46,6 +46,7 @@ if str(ROOT) not in sys.path:
 HIDDEN, HEADS, HEAD_DIM, FFN = 3072, 24, 128, 8192
 METRIC = "dit_block_ms"
 SMALL_TOKENS = 23638           # the benchmark's second token count, timed in the same run
+NVLINK_PEER_GBS = 770.0
 INT8_NOMINAL_TOPS = 4500.0     # dense INT8, nominal; no measured INT8 peak exists on this pool
 KERNEL_CHOICES = ["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant",
                   "rope_pack", "quant_gathered", "gemm_out_residual", "gemm_fc2", "gemm_fc2_residual",
@@ -65,6 +66,9 @@ def parse():
                     help="gated residuals as their own kernel instead of in the GEMM epilogue")
     ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the kernels one by one")
     ap.add_argument("--no-sp-check", action="store_true", help="skip the 1-GPU-vs-N-GPU parity gate")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "all_to_all"],
+                    help="N > 1: how q/k/v and the attention output cross ranks: the kernels' own stores "
+                         "into peer memory, or all-to-all collectives")
     ap.add_argument("--no-small", action="store_true", help=f"skip the {SMALL_TOKENS}-token leg")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table (N=1)")
     ap.add_argument("--kernel", default=None, choices=KERNEL_CHOICES,
@@ -254,8 +258,9 @@ def workload_config(tokens):
 class Job:
     """One rank's view of the block at a token count: shard bounds, block, rotary tables."""
 
-    def __init__(self, pkg, params, tokens, world, rank, dev, head_chunks, fuse_residual):
+    def __init__(self, pkg, params, tokens, world, rank, dev, head_chunks, fuse_residual, exchange="all_to_all"):
         self.pkg, self.tokens, self.world, self.rank, self.dev = pkg, tokens, world, rank, dev
+        self.exchange, self.exchange_note = ("all_to_all" if world > 1 else None), None
         self.splits = pkg.ulysses.sequence_splits(tokens, world)
         self.L = self.splits[rank]
         self.row0 = sum(self.splits[:rank])
@@ -266,6 +271,13 @@ class Job:
         chunks = head_chunks or (1 if world == 1 else pkg.ulysses.choose_head_chunks(tokens, local_heads))
         while local_heads % chunks:
             chunks -= 1
+        if world > 1 and exchange == "peer":
+            # collective: succeeds or raises on every rank alike
+            try:
+                self.sp.enable_peer_exchange(dev)
+                self.exchange, chunks = "peer", 1
+            except RuntimeError as exc:
+                self.exchange_note = f"peer exchange unavailable, using all-to-all collectives: {exc}"
         self.chunks = chunks
         self.params = params
         self.block = pkg.block.DiTBlock(params, sp=self.sp, head_chunks=chunks, overlap=True,
@@ -284,6 +296,17 @@ class Job:
 
     def shard(self, full):
         return full[self.row0:self.row0 + self.L].contiguous()
+
+    def parallelism(self):
+        if self.world == 1:
+            return None
+        how = "peer_stores" if self.exchange == "peer" else f"all_to_all_headchunks{self.chunks}"
+        return f"ulysses_sp{self.world}_{how}"
+
+    def close(self):
+        if self.sp is not None and self.sp.peer is not None:
+            self.sp.peer.close()
+            self.sp.peer = None
 
 
 def sp_check(job: Job, dist) -> dict:
@@ -331,7 +354,7 @@ def sp_check(job: Job, dist) -> dict:
     dist.all_reduce(rows_t, op=dist.ReduceOp.SUM)
     err, ref_max = -float(stats[3]), -float(stats[4])
     tol = max(2e-4, 2.0 ** -7 * ref_max)
-    out = {"tokens": T, "world": job.world, "head_chunks": job.chunks,
+    out = {"tokens": T, "world": job.world, "head_chunks": job.chunks, "exchange": job.exchange,
            "bitwise_equal": bool(stats[0] == 1.0), "attention_rows_bitwise_equal": bool(stats[1] == 1.0),
            "psnr_db": None if float(stats[2]) >= 1e9 else float(stats[2]),
            "psnr_note": "null = infinite (no differing element on any rank)",
@@ -419,6 +442,11 @@ def kernel_row(label, entry, ms, bound, work, pk):
     elif bound == "bf16":
         row.update(unit="TFLOP/s", achieved=work / ms / 1e9, peak=pk["bf16_sustained"],
                    peak_kind=f"dense bf16 sustained, {pk['source']}")
+    elif bound == "nvlink":
+        # bytes this GPU stores into its peers' memory; 770 GB/s is the peer-copy rate per
+        # direction measured on this pool's B200s (nominal 900)
+        row.update(unit="GB/s", achieved=work / ms / 1e6, peak=NVLINK_PEER_GBS,
+                   peak_kind="NVLink peer copy per direction, measured on this pool (nominal 900)")
     if "achieved" in row:
         row["frac"] = row["achieved"] / row["peak"]
     return row
@@ -467,7 +495,7 @@ def run_b200(args):
 
     T = args.tokens
     params = pkg.block.make_block_params(HIDDEN, HEADS, HEAD_DIM, FFN, seed=0, device=dev)
-    job = Job(pkg, params, T, world, rank, dev, args.head_chunks, not args.no_fuse_residual)
+    job = Job(pkg, params, T, world, rank, dev, args.head_chunks, not args.no_fuse_residual, args.exchange)
     blk, cos, sin, L = job.block, job.cos, job.sin, job.L
     timing = Timing(dev, world, dist)
 
@@ -604,7 +632,8 @@ def run_b200(args):
     small = None
     if T != SMALL_TOKENS and not args.no_small:
         torch.cuda.empty_cache()
-        job2 = Job(pkg, params, SMALL_TOKENS, world, rank, dev, args.head_chunks, not args.no_fuse_residual)
+        job2 = Job(pkg, params, SMALL_TOKENS, world, rank, dev, args.head_chunks, not args.no_fuse_residual,
+                   args.exchange)
         if world > 1 and not args.no_sp_check:
             checks.append(sp_check(job2, dist))
             if not checks[-1]["passed"]:
@@ -621,8 +650,10 @@ def run_b200(args):
             step2 = pkg.block.GraphedBlock(job2.block, x2, job2.cos, job2.sin).replay
         t2 = timing.rounds(step2, max(11, args.steps))
         small = {"tokens": SMALL_TOKENS, "ms": t2["median"], "timing": t2, "head_chunks": job2.chunks,
-                 "parallelism": (f"ulysses_sp{world}_headchunks{job2.chunks}" if world > 1 else
+                 "parallelism": (job2.parallelism() if world > 1 else
                                  ("single_gpu_cuda_graph" if not args.no_graph else "single_gpu"))}
+        if job2.exchange_note:
+            small["exchange_note"] = job2.exchange_note
         if kernels is not None:
             small["kernels"] = kernel_table(pkg, job2.block, x2, job2.cos, job2.sin, pk, passes=5)
             small["kernels_ms_sum"] = sum(k["ms"] for k in small["kernels"])
@@ -630,6 +661,9 @@ def run_b200(args):
                 small["kernels"] += standalone_rows(pkg, SMALL_TOKENS, dev, pk)
         ops.check_device_status(dev)
 
+    if small is not None:
+        job2.close()
+    job.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -655,8 +689,7 @@ def run_b200(args):
         # clock-normalised: fraction of what the tensor pipe can do at the sampled SM clock
         roofline["frac_of_pipe_at_sampled_clock"] = (
             roofline["achieved"] * 1e12 / (8192.0 * 148 * clocks["sm_mhz"] * 1e6))
-    par = (f"ulysses_sp{world}_headchunks{job.chunks}" if world > 1
-           else ("single_gpu_cuda_graph" if use_graph else "single_gpu"))
+    par = job.parallelism() if world > 1 else ("single_gpu_cuda_graph" if use_graph else "single_gpu")
     line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8 GEMMs (s32 accumulate) + bf16 attention (f32 accumulate)",
@@ -673,6 +706,8 @@ def run_b200(args):
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
             "attn_tflops_per_gpu": roofline["achieved"],
             "int8_ops_per_step": int8_ops}
+    if job.exchange_note:
+        line["exchange_note"] = job.exchange_note
     if checks:
         line["sp_check"] = checks[0]
         if len(checks) > 1:

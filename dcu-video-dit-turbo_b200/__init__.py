@@ -16,6 +16,6 @@ import sys as _sys
 
 _sys.modules.setdefault("dcu_video_dit_turbo_b200", _sys.modules[__name__])
 
-from . import _lib, ops, gates, linear, attention, ulysses, block, dispatch, save, vae_sp  # noqa: E402,F401
+from . import _lib, ops, gates, linear, attention, peer, ulysses, block, dispatch, save, vae_sp  # noqa: E402,F401
 
-__all__ = ["_lib", "ops", "gates", "linear", "attention", "ulysses", "block", "dispatch", "save", "vae_sp"]
+__all__ = ["_lib", "ops", "gates", "linear", "attention", "peer", "ulysses", "block", "dispatch", "save", "vae_sp"]

@@ -42,6 +42,13 @@ SYMBOLS = {
     "b2_qk_norm_rope": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp]),
     "b2_qk_norm_rope_pack": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
     "b2_quantize_int8_rowwise_gathered": (_int, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "b2_peer_alloc": (_int, [_i64, _vp]),
+    "b2_peer_free": (_int, [_vp]),
+    "b2_peer_export": (_int, [_vp, _vp, _i32]),
+    "b2_peer_open": (_int, [_vp, _i32, _vp]),
+    "b2_peer_close": (_int, [_vp]),
+    "b2_qk_norm_rope_scatter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i64, _f32, _vp]),
+    "b2_copy_segments": (_int, [_vp, _vp, _vp, _i32, _vp]),
     "b2_images_to_u8": (_int, [_vp, _i32, _vp, _i64, _vp]),
     "b2_gate_residual": (_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
 }

@@ -119,9 +119,16 @@ class DiTBlock:
         if self.sp is not None and self.sp.world > 1:
             # sequence parallel: norm + rotary write the all-to-all send buffer directly and
             # the out-projection's quantizer reads the reverse all-to-all's buffer in place
-            send = ops.qk_norm_rope_pack(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin,
-                                         self.sp.world, self.head_chunks)
-            gathered = self.sp.attention_packed(send, self._attn, overlap=self.overlap)
+            if self.sp.peer is not None:
+                # the kernels carry the exchange: stores into the owner ranks' buffers
+                gathered = self.sp.attention_peer(
+                    lambda table, row0, seq: ops.qk_norm_rope_scatter(
+                        qkv, p["q_norm_w"], p["k_norm_w"], cos, sin, table, self.sp.world, row0, seq),
+                    self._attn)
+            else:
+                send = ops.qk_norm_rope_pack(qkv, p["q_norm_w"], p["k_norm_w"], cos, sin,
+                                             self.sp.world, self.head_chunks)
+                gathered = self.sp.attention_packed(send, self._attn, overlap=self.overlap)
             if taps is not None:
                 taps["attn"] = UlyssesSP.unpack_gathered(gathered).contiguous()
             q8, s = ops.quantize_int8_rowwise_gathered(gathered)

@@ -16,7 +16,7 @@ CSRC = HERE / "csrc"
 OUT = HERE / "libb2dit.so"
 STAMP = HERE / "libb2dit.so.srchash"
 SOURCES = ["abi.cu", "quantize.cu", "elementwise.cu", "norm.cu", "int8_gemm.cu", "int8_gemm_2cta.cu", "flash_fwd.cu",
-           "flash_fwd_2cta.cu", "int8_linear_static.cu"]
+           "flash_fwd_2cta.cu", "int8_linear_static.cu", "peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",

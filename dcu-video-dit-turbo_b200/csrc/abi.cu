@@ -209,6 +209,31 @@ int b2_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const void
   return launch_qk_norm_rope_pack(qkv, send, qw, kw, cos_tab, sin_tab, L, H, world, chunks, eps, (cudaStream_t)stream);
 }
 
+int b2_qk_norm_rope_scatter(const void* qkv, void* const* recv_bases, const void* qw, const void* kw,
+                            const float* cos_tab, const float* sin_tab, int64_t L, int32_t H,
+                            int32_t world, int32_t chunks, int64_t row0, int64_t S, float eps,
+                            void* stream) {
+  if (L < 0 || H <= 0 || world <= 0 || chunks <= 0 || H % (world * chunks) != 0)
+    return fail(B2_BAD_SHAPE, "qk_norm_rope_scatter: world*chunks must divide the head count (L=%lld H=%d world=%d chunks=%d)",
+                (long long)L, H, world, chunks);
+  if (world > 8) return fail(B2_NOT_WHITELISTED, "qk_norm_rope_scatter: at most 8 ranks (world=%d)", world);
+  if (row0 < 0 || S < 0 || row0 + L > S)
+    return fail(B2_BAD_SHAPE, "qk_norm_rope_scatter: rows [%lld, %lld) do not fit a sequence of %lld",
+                (long long)row0, (long long)(row0 + L), (long long)S);
+  if (L == 0) return B2_OK;
+  if (!qkv || !recv_bases || !qw || !kw || !cos_tab || !sin_tab) return fail(B2_NULL_POINTER, "qk_norm_rope_scatter: null pointer");
+  if (!aligned16(qkv) || !aligned16(qw) || !aligned16(kw) || !aligned16(cos_tab) || !aligned16(sin_tab))
+    return fail(B2_BAD_STRIDE, "qk_norm_rope_scatter: pointers must be 16-byte aligned");
+  for (int p = 0; p < world; ++p) {
+    if (!recv_bases[p]) return fail(B2_NULL_POINTER, "qk_norm_rope_scatter: receive buffer of rank %d is null", p);
+    if (!aligned16(recv_bases[p])) return fail(B2_BAD_STRIDE, "qk_norm_rope_scatter: receive buffer of rank %d is not 16-byte aligned", p);
+    if (recv_bases[p] == qkv) return fail(B2_BAD_STRIDE, "qk_norm_rope_scatter: a receive buffer must not alias the input");
+  }
+  if (!(eps >= 0.f)) return fail(B2_BAD_SHAPE, "qk_norm_rope_scatter: eps must be non-negative");
+  return launch_qk_norm_rope_scatter(qkv, recv_bases, qw, kw, cos_tab, sin_tab, L, H, world, chunks, row0, S,
+                                     eps, (cudaStream_t)stream);
+}
+
 int b2_quantize_int8_rowwise_gathered(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                                       int32_t world, int32_t chunks, void* stream) {
   if (M < 0 || K <= 0 || world <= 0 || chunks <= 0 || K % ((int64_t)world * chunks * 8) != 0 || K > 16384)

@@ -29,6 +29,12 @@ int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* 
 int launch_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const void* kw,
                              const float* cos_tab, const float* sin_tab, int64_t L, int H, int world,
                              int chunks, float eps, cudaStream_t stream);
+// recv_bases: host array of `world` device pointers (each rank's receive buffer as mapped here)
+int launch_qk_norm_rope_scatter(const void* qkv, void* const* recv_bases, const void* qw, const void* kw,
+                                const float* cos_tab, const float* sin_tab, int64_t L, int H, int world,
+                                int chunks, int64_t row0, int64_t S, float eps, cudaStream_t stream);
+int launch_copy_segments(const void* const* src, void* const* dst, const int64_t* bytes, int n,
+                         cudaStream_t stream);
 // out_i32 != nullptr: plain int32 result.  Otherwise the fused dequant epilogue writes
 // bf16 to out_bf16, or, with gate/residual non-null, x = bf16(x + bf16(gate*y)) in place.
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,

@@ -187,6 +187,7 @@ __device__ __forceinline__ uint4 norm_rope_vec8(const uint4 v, const uint4 wv, c
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+constexpr int kRopeMaxPeers = 8;  // ranks of one NVSwitch domain the scatter kernel addresses
 constexpr int kRopeMaxIter = 6;   // 16-byte vectors of one row per thread (template ITER): heads <= 32
 
 // qkv bf16 [S,3,H,128], q and k normed and rotated in place.  One CTA walks rows; a thread
@@ -315,6 +316,60 @@ int launch_layernorm_mod(const void* x, const void* scale, const void* shift, vo
   return check_launch("layernorm_mod");
 }
 
+// The packing kernel with the sequence-parallel exchange folded in: instead of a local send
+// buffer that an all-to-all then moves, every vector goes straight to the rank that owns its
+// head, into that rank's receive buffer [chunks, S, c, 3, 128] at row row0 + s (plain 16-byte
+// stores through peer pointers; dst.base[rank] is this GPU's own buffer).  A (head, part) is
+// 256 contiguous bytes at the destination.  Same arithmetic as the other two kernels.
+struct RopePeerBases {
+  uint4* base[kRopeMaxPeers];
+};
+
+template <int ITER>
+__global__ void __launch_bounds__(kThreads)
+qk_norm_rope_scatter_kernel(const uint4* __restrict__ qkv, const __grid_constant__ RopePeerBases dst,
+                            const uint4* __restrict__ qw, const uint4* __restrict__ kw,
+                            const float4* __restrict__ cos_tab, const float4* __restrict__ sin_tab,
+                            int64_t L, int H, int world, int chunks, int64_t row0, int64_t S, float eps) {
+  const int row_vec = 3 * H * 16;
+  const int c_heads = H / (world * chunks);
+  const int l = threadIdx.x & 15;
+  const uint32_t group_mask = 0xffffu << (threadIdx.x & 16);
+  const uint4 wq = qw[l], wk = kw[l];
+  // where vector i of this rank's row 0 lands, and the distance between rows there
+  uint4* dst0[ITER];
+  int part_of[ITER];
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int i = threadIdx.x + it * kThreads;
+    dst0[it] = nullptr;
+    part_of[it] = 3;   // dead
+    if (i < row_vec) {
+      const int hp = i >> 4, part = hp / H, h = hp - part * H;
+      const int seg = h / c_heads, ci = h - seg * c_heads;     // seg = p*chunks + ch
+      const int p = seg / chunks, ch = seg - p * chunks;
+      dst0[it] = dst.base[p] + ((((int64_t)ch * S + row0) * c_heads + ci) * 3 + part) * 16 + l;
+      part_of[it] = part;
+    }
+  }
+  const int64_t dst_row = (int64_t)c_heads * 3 * 16;
+  for (int64_t s = blockIdx.x; s < L; s += gridDim.x) {
+    const uint4* row = qkv + s * row_vec;
+    const float4 c = cos_tab[s * 16 + l], sn = sin_tab[s * 16 + l];
+    uint4 v[ITER];
+#pragma unroll
+    for (int it = 0; it < ITER; ++it)
+      if (part_of[it] < 3) v[it] = ldg_stream(row + threadIdx.x + it * kThreads);
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      if (part_of[it] == 3) continue;
+      const uint4 o = part_of[it] == 2 ? v[it]
+                                       : norm_rope_vec8(v[it], part_of[it] == 1 ? wk : wq, c, sn, eps, group_mask);
+      dst0[it][s * dst_row] = o;
+    }
+  }
+}
+
 int launch_qk_norm_rope(void* qkv, const void* qw, const void* kw, const float* cos_tab,
                         const float* sin_tab, int64_t S, int H, float eps, cudaStream_t stream) {
   if (3 * H * 16 > kRopeMaxIter * kThreads)
@@ -356,6 +411,33 @@ int launch_qk_norm_rope_pack(const void* qkv, void* send, const void* qw, const 
   }
 #undef B2_ROPE_PACK
   return check_launch("qk_norm_rope_pack");
+}
+
+int launch_qk_norm_rope_scatter(const void* qkv, void* const* recv_bases, const void* qw, const void* kw,
+                                const float* cos_tab, const float* sin_tab, int64_t L, int H, int world,
+                                int chunks, int64_t row0, int64_t S, float eps, cudaStream_t stream) {
+  if (3 * H * 16 > kRopeMaxIter * kThreads)
+    return fail(B2_NOT_WHITELISTED, "qk_norm_rope_scatter: at most %d heads", kRopeMaxIter * kThreads / 48);
+  if (world > kRopeMaxPeers)
+    return fail(B2_NOT_WHITELISTED, "qk_norm_rope_scatter: at most %d ranks", kRopeMaxPeers);
+  RopePeerBases dst;
+  for (int p = 0; p < kRopeMaxPeers; ++p) dst.base[p] = (uint4*)(p < world ? recv_bases[p] : nullptr);
+  const int64_t cap = (int64_t)kNumSMsB200 * 8;
+  const int64_t blocks = L < cap ? L : cap;
+#define B2_ROPE_SCATTER(ITER)                                                                     \
+  qk_norm_rope_scatter_kernel<ITER><<<(int)blocks, kThreads, 0, stream>>>(                        \
+      (const uint4*)qkv, dst, (const uint4*)qw, (const uint4*)kw, (const float4*)cos_tab,         \
+      (const float4*)sin_tab, L, H, world, chunks, row0, S, eps)
+  switch ((3 * H * 16 + kThreads - 1) / kThreads) {   // vectors of one row per thread
+    case 1: B2_ROPE_SCATTER(1); break;
+    case 2: B2_ROPE_SCATTER(2); break;
+    case 3: B2_ROPE_SCATTER(3); break;
+    case 4: B2_ROPE_SCATTER(4); break;
+    case 5: B2_ROPE_SCATTER(5); break;
+    default: B2_ROPE_SCATTER(6); break;
+  }
+#undef B2_ROPE_SCATTER
+  return check_launch("qk_norm_rope_scatter");
 }
 
 }  // namespace b2

@@ -440,6 +440,53 @@ def qk_norm_rope_pack(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch
     return send
 
 
+def qk_norm_rope_scatter(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor,
+                         cos: torch.Tensor, sin: torch.Tensor, recv_table, world: int, row0: int,
+                         sequence: int, chunks: int = 1, eps: float = 1e-6) -> None:
+    """qk_norm_rope_pack with the exchange folded in: every (head, part) of this rank's rows
+    is stored straight into the receive buffer bf16 [chunks, S, c, 3, 128] of the rank that
+    owns the head, at row `row0 + l`.  `recv_table` is a C array of `world` device addresses
+    (peer.PeerBuffer.table).  Nothing waits: the caller orders the ranks (peer.PeerExchange)."""
+    _require(qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 4
+             and qkv.is_contiguous() and qkv.shape[1] == 3 and qkv.shape[3] == 128,
+             "qkv must be a contiguous CUDA bf16 [L,3,H,128] tensor")
+    L, _, h, _ = qkv.shape
+    _require(0 < world <= 8 and chunks > 0 and h % (world * chunks) == 0,
+             "world*chunks must divide the head count, with at most 8 ranks")
+    _require(len(recv_table) == world, "one receive buffer per rank")
+    _require(0 <= row0 and row0 + L <= sequence, "this rank's rows must lie inside the sequence")
+    _require(tuple(cos.shape) == (L, 64) and tuple(sin.shape) == (L, 64), "cos/sin must be fp32 [L,64]")
+    _require_vector(cos, qkv, L * 64, torch.float32, "cos")
+    _require_vector(sin, qkv, L * 64, torch.float32, "sin")
+    _require_vector(q_weight, qkv, 128, torch.bfloat16, "q norm weight")
+    _require_vector(k_weight, qkv, 128, torch.bfloat16, "k norm weight")
+    if L:
+        _call("b2_qk_norm_rope_scatter", qkv, qkv.data_ptr(), recv_table, q_weight.data_ptr(),
+              k_weight.data_ptr(), cos.data_ptr(), sin.data_ptr(), L, h, world, chunks, row0, sequence,
+              eps, _stream(qkv),
+              work=("nvlink", 6 * L * h * 128 * (world - 1) // world) if world > 1
+              else ("hbm", 12 * L * h * 128 + 512 * L))
+
+
+def copy_segments(src: torch.Tensor, src_offsets, src_table, dst_table, bytes_table, n: int,
+                  total_bytes: int, remote_bytes: int = 0) -> None:
+    """One launch copying n <= 8 contiguous byte ranges of `src` (at `src_offsets`, bytes) to
+    the device addresses in `dst_table` (local or peer-mapped); the tables are C arrays,
+    `src_table` is scratch that this call fills.  `remote_bytes` (of `total_bytes`) go to other
+    GPUs: when non-zero the launch is accounted against the link, not against local memory."""
+    _require(src.is_cuda and src.is_contiguous(), "source must be a contiguous CUDA tensor")
+    _require(0 <= n <= 8 and len(src_offsets) == n, "at most 8 segments")
+    base = src.data_ptr()
+    limit = src.numel() * src.element_size()
+    for i in range(n):
+        _require(0 <= src_offsets[i] and src_offsets[i] + bytes_table[i] <= limit,
+                 "a segment reaches outside the source tensor")
+        src_table[i] = base + src_offsets[i]
+    if n and total_bytes:
+        _call("b2_copy_segments", src, src_table, dst_table, bytes_table, n, _stream(src),
+              work=("nvlink", remote_bytes) if remote_bytes else ("hbm", 2 * total_bytes))
+
+
 def quantize_int8_rowwise_gathered(x: torch.Tensor):
     """The rowwise quantizer reading the reverse all-to-all's receive buffer in place:
     x bf16 [chunks, world, M, w] (or [chunks, world, M, c, D]) holds row m's columns ((p*chunks + ch)*w ...) in segment

@@ -13,7 +13,10 @@ generalised from 2 ranks to any world size dividing the head count.
 
 Works on the NCCL backend (CUDA tensors, NVLink) and on gloo (CPU tensors; used
 by the layout tests).  Received data always lands in local memory before a kernel
-reads it; no kernel here touches a peer's memory.
+reads it.  Two transports carry the same layouts: all-to-all collectives
+(`attention_packed`), and, for the ranks of one machine, the kernels' own stores into the
+destination rank's memory (`enable_peer_exchange` + `attention_peer`; peer.py), which
+removes both all-to-alls and their pack / unpack passes from the step.
 """
 from __future__ import annotations
 
@@ -21,6 +24,8 @@ from typing import Callable, Sequence
 
 import torch
 import torch.distributed as dist
+
+from .peer import PeerExchange
 
 
 def sequence_splits(seq: int, world: int) -> tuple[int, ...]:
@@ -67,7 +72,43 @@ class UlyssesSP:
         self.heads = heads
         self.local_heads = heads // self.world
         self.dim = dim
+        self.row0 = sum(self.splits[:self.rank])
         self._comm_stream = None
+        self.peer: PeerExchange | None = None
+
+    # -- exchange through peer memory ---------------------------------------------------
+    def enable_peer_exchange(self, device: torch.device) -> PeerExchange:
+        """Allocate and map the peer buffers of this group (collective; all ranks on one
+        machine with peer access between their GPUs).  Raises RuntimeError when a buffer
+        cannot be allocated or mapped; the all-to-all path stays usable then."""
+        if self.peer is None:
+            self.peer = PeerExchange(self.splits, self.heads, self.dim, device, self.group)
+        return self.peer
+
+    def attention_peer(self, scatter: Callable, attn: Callable) -> torch.Tensor:
+        """Sequence-parallel attention without all-to-all collectives.
+
+        `scatter(recv_table, row0, sequence)` must launch ops.qk_norm_rope_scatter for this
+        rank's rows (it stores q, k, v of every head into the owner rank's receive buffer).
+        Then: rank barrier, attention over the H/P local heads on the local receive buffer,
+        one copy kernel that pushes every owner's rows of the output into its gathered buffer,
+        rank barrier.  Returns the gathered buffer [1, P, L_r, H/P, D] (same layout as
+        `attention_packed` with one chunk), which is REUSED by the next call.
+
+        Everything runs on the current stream, and a step's calls must be issued on the same
+        stream on every rank: the second barrier of step t orders every rank's attention
+        reads before any rank's scatter of step t+1, and the first barrier of step t+1 orders
+        every rank's reads of the gathered buffer before any push of step t+1."""
+        pe = self.peer
+        if pe is None:
+            raise RuntimeError("enable_peer_exchange() has not been called on this group")
+        scatter(pe.recv_buffer.table, self.row0, self.sequence)
+        pe.barrier()
+        out = attn(*self.chunk_views(pe.recv[0]))                  # [1,c,S,D] view of [1,S,c,D]
+        rows = out.transpose(1, 2).reshape(self.sequence, self.local_heads, self.dim)
+        pe.push(rows)
+        pe.barrier()
+        return pe.result
 
     # -- plain transforms ----------------------------------------------------------
     def sequence_to_heads(self, tensor: torch.Tensor) -> torch.Tensor:

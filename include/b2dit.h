@@ -198,6 +198,42 @@ int b2_qk_norm_rope_pack(const void* qkv_bf16, void* send_bf16, const void* q_we
 int b2_quantize_int8_rowwise_gathered(const void* x_bf16, int8_t* q, float* scale, int64_t M,
                                       int64_t K, int32_t world, int32_t chunks, void* stream);
 
+/* The same exchange carried by the kernels themselves over peer memory, for ranks of one
+ * NVSwitch domain (at most 8).  These entry points have no counterpart in the reference, whose
+ * sequence-parallel model moves the layouts above with torch.distributed all-to-all calls
+ * (benchmarks/bench_sp_head_chunk_overlap.py:140-193); the bytes that arrive are the same.
+ *
+ * b2_peer_alloc / b2_peer_free: a zero-filled device buffer of the CURRENT device that other
+ * processes may map (plain cudaMalloc, outside any caching allocator).  b2_peer_export fills
+ * a 64-byte handle for it; b2_peer_open maps a handle exported by another process of the
+ * same machine (peer access is enabled on first use) and b2_peer_close unmaps it.  Set-up
+ * and tear-down only: these are the only entry points of the library that allocate, map or
+ * free device memory, and they synchronise the device.
+ *
+ * b2_qk_norm_rope_scatter: b2_qk_norm_rope_pack writing every vector straight into the
+ * receive buffer of the rank that owns its head: recv_bases is a HOST array of `world`
+ * device pointers, entry p being rank p's buffer bf16 [chunks][S][c][3][128] as mapped in this
+ * process (the caller's own buffer at its own index); this rank's row l lands at row row0 + l.
+ * Plain 16-byte stores; nothing waits.  The caller orders the ranks: every rank's scatter
+ * must have completed before any rank reads its buffer, and all reads before the next scatter
+ * (e.g. a collective on the same stream in between).
+ *
+ * b2_copy_segments: n <= 8 contiguous copies (16-byte aligned, sizes multiples of 16) in one
+ * launch; sources and destinations may be local or peer-mapped.  Used for the reverse
+ * direction: rows [row0_p, row0_p + L_p) of the attention output go to slot [ch][me] of rank
+ * p's buffer bf16 [chunks][world][L_p][c][128], which b2_quantize_int8_rowwise_gathered reads. */
+int b2_peer_alloc(int64_t bytes, void** ptr);
+int b2_peer_free(void* ptr);
+int b2_peer_export(void* ptr, void* handle, int32_t handle_bytes);
+int b2_peer_open(const void* handle, int32_t handle_bytes, void** ptr);
+int b2_peer_close(void* ptr);
+int b2_qk_norm_rope_scatter(const void* qkv_bf16, void* const* recv_bases, const void* q_weight_bf16,
+                            const void* k_weight_bf16, const float* cos_tab, const float* sin_tab,
+                            int64_t L, int32_t H, int32_t world, int32_t chunks, int64_t row0,
+                            int64_t S, float eps, void* stream);
+int b2_copy_segments(const void* const* src, void* const* dst, const int64_t* bytes, int32_t n,
+                     void* stream);
+
 /* Decoded frames -> RGB24 bytes for the video encoder, the whole clip in one launch:
  * out[i] = uint8(clamp(images[i] * 255, 0, 255)), product rounded to the input type, cast
  * truncating, NaN -> 0.  Replaces the per-frame `(image * 255).clamp(0, 255).byte()` + copy

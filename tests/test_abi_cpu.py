@@ -66,6 +66,28 @@ def test_argument_validation_precedes_launch(pkg):
     assert lib.b2_layernorm_mod(fake, fake, fake, fake, 4, 12, 1e-6, None) == 4
     assert lib.b2_qk_norm_rope(fake, fake, fake, fake, fake, 4, 0, 1e-6, None) == 2
     assert lib.b2_gate_residual(fake, None, fake, 4, 8, None) == 7
+    # peer exchange: tables are checked entry by entry before anything is launched
+    two = (P * 2)(0x1000, 0x2000)
+    assert lib.b2_qk_norm_rope_scatter(fake, two, fake, fake, fake, fake, 4, 24, 2, 1, 0, 8, 1e-6, None) == 3   # aliases the input
+    assert lib.b2_qk_norm_rope_scatter(P(0x3000), two, fake, fake, fake, fake, 4, 24, 5, 1, 0, 8, 1e-6, None) == 2
+    assert lib.b2_qk_norm_rope_scatter(P(0x3000), two, fake, fake, fake, fake, 4, 24, 2, 1, 6, 8, 1e-6, None) == 2
+    assert b"do not fit a sequence" in lib.b2_last_error()
+    assert lib.b2_qk_norm_rope_scatter(P(0x3000), (P * 2)(0x1000, 0), fake, fake, fake, fake, 4, 24, 2, 1, 0, 8,
+                                       1e-6, None) == 7
+    assert lib.b2_qk_norm_rope_scatter(P(0x3000), (P * 2)(0x1000, 0x2004), fake, fake, fake, fake, 4, 24, 2, 1, 0,
+                                       8, 1e-6, None) == 3
+    assert lib.b2_qk_norm_rope_scatter(P(0x3000), (P * 2)(0x1000, 0x3000), fake, fake, fake, fake, 4, 24, 2, 1, 0,
+                                       8, 1e-6, None) == 3
+    assert lib.b2_qk_norm_rope_scatter(P(0x3000), two, fake, fake, fake, fake, 0, 24, 2, 1, 0, 8, 1e-6, None) == 0
+    assert lib.b2_copy_segments(two, two, (ctypes.c_int64 * 2)(16, 24), 2, None) == 2
+    assert lib.b2_copy_segments(two, two, (ctypes.c_int64 * 2)(0, 0), 2, None) == 0     # nothing to copy, nothing launched
+    assert lib.b2_copy_segments(None, two, (ctypes.c_int64 * 2)(16, 16), 2, None) == 7
+    assert lib.b2_copy_segments(two, two, (ctypes.c_int64 * 2)(16, 16), 9, None) == 2
+    assert lib.b2_peer_alloc(-1, ctypes.byref(P())) == 2
+    assert lib.b2_peer_alloc(16, None) == 7
+    assert lib.b2_peer_export(None, fake, 64) == 7
+    assert lib.b2_peer_open(fake, 12, ctypes.byref(P())) == 2
+    assert lib.b2_peer_free(None) == 0 and lib.b2_peer_close(None) == 0
 
 
 def test_missing_library_fails_loudly(pkg, tmp_path):

@@ -79,8 +79,24 @@ def _worker(rank, world, port, seq, result_dir):
         ops.check_device_status(dev)
         block_equal = torch.equal(y_sp, y_single[sl])
         psnr = ref.psnr(y_single[sl].float().cpu(), y_sp.float().cpu())
+        # the same block with the exchange carried by the kernels' own stores into the
+        # destination ranks' memory instead of all-to-all collectives: three steps in a row on
+        # different inputs, so that reuse of the peer buffers by the next step is exercised
+        sp.enable_peer_exchange(dev)
+        peer_blk = pkg.block.DiTBlock(params, sp=sp)
+        peer_equal = []
+        for step in range(3):
+            xs = (x_full.float() * (1.0 + 0.25 * step)).to(torch.bfloat16)
+            want = pkg.block.DiTBlock(params).forward(xs.to(dev), cos.to(dev), sin.to(dev))[sl]
+            got = peer_blk.forward(xs[sl].to(dev), cos[sl].to(dev), sin[sl].to(dev))
+            torch.cuda.synchronize()
+            peer_equal.append(bool(torch.equal(got, want)))
+        ops.check_device_status(dev)
+        dist.barrier()
+        sp.peer.close()
         Path(result_dir, f"r{rank}.txt").write_text(
-            f"attn_all_ranks={int(flag.item())} bad={bad} block_equal={block_equal} psnr={psnr}")
+            f"attn_all_ranks={int(flag.item())} bad={bad} block_equal={block_equal} psnr={psnr} "
+            f"peer_equal={peer_equal}")
     finally:
         dist.destroy_process_group()
 
@@ -104,9 +120,10 @@ def test_ulysses_attention_and_block_bitwise_vs_single_gpu(tmp_path, seq):
         # row-local int8 stages and per-head attention are partition invariant, so the block
         # is expected bitwise equal; the published gate is PSNR (>= 60 dB, this project's
         # choice: the reference gives no block-level threshold)
-        psnr = float(text.split("psnr=")[1])
+        psnr = float(text.split("psnr=")[1].split()[0])
         assert psnr >= 60.0, text
         assert "block_equal=True" in text, text
+        assert "peer_equal=[True, True, True]" in text, text
 
 
 def test_second_device_in_the_same_process(cuda_pkg, ref):
