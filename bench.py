@@ -477,6 +477,32 @@ def standalone_rows(pkg, tokens, dev, pk):
     return rows
 
 
+def checked_job(pkg, params, tokens, world, rank, dev, args, dist, checks):
+    """A Job at `tokens` that has passed the parity gate (N > 1), or exit 2.  If the peer
+    exchange fails the gate, that is recorded in `exchange_note` (and in the failed check kept
+    beside it) and the job is rebuilt on all-to-all collectives, which must then pass."""
+    job = Job(pkg, params, tokens, world, rank, dev, args.head_chunks, not args.no_fuse_residual, args.exchange)
+    if world == 1 or args.no_sp_check:
+        return job
+    check = sp_check(job, dist)
+    pkg.ops.check_device_status(dev)
+    if not check["passed"] and job.exchange == "peer":
+        failed = check
+        job.close()
+        job = Job(pkg, params, tokens, world, rank, dev, args.head_chunks, not args.no_fuse_residual, "all_to_all")
+        job.exchange_note = "the peer exchange FAILED the parity gate; timed with all-to-all collectives instead"
+        check = sp_check(job, dist)
+        check["failed_peer_check"] = failed
+    checks.append(check)
+    if not check["passed"]:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "n_gpus": world, "error": "sequence-parallel output differs "
+                              "from the single-GPU block", "sp_check": check}))
+        dist.destroy_process_group()
+        sys.exit(2)
+    return job
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -495,21 +521,11 @@ def run_b200(args):
 
     T = args.tokens
     params = pkg.block.make_block_params(HIDDEN, HEADS, HEAD_DIM, FFN, seed=0, device=dev)
-    job = Job(pkg, params, T, world, rank, dev, args.head_chunks, not args.no_fuse_residual, args.exchange)
-    blk, cos, sin, L = job.block, job.cos, job.sin, job.L
-    timing = Timing(dev, world, dist)
-
     # ---- parity gate inside the distributed run (before anything is timed) ----
     checks = []
-    if world > 1 and not args.no_sp_check:
-        checks.append(sp_check(job, dist))
-        ops.check_device_status(dev)
-        if not checks[-1]["passed"]:
-            if rank == 0:
-                print(json.dumps({"metric": METRIC, "n_gpus": world, "error": "sequence-parallel output differs "
-                                  "from the single-GPU block", "sp_check": checks[-1]}))
-            dist.destroy_process_group()
-            sys.exit(2)
+    job = checked_job(pkg, params, T, world, rank, dev, args, dist, checks)
+    blk, cos, sin, L = job.block, job.cos, job.sin, job.L
+    timing = Timing(dev, world, dist)
 
     x_dev = job.shard(job.full_input(1234))
     x_host = x_dev.cpu().pin_memory()
@@ -632,16 +648,7 @@ def run_b200(args):
     small = None
     if T != SMALL_TOKENS and not args.no_small:
         torch.cuda.empty_cache()
-        job2 = Job(pkg, params, SMALL_TOKENS, world, rank, dev, args.head_chunks, not args.no_fuse_residual,
-                   args.exchange)
-        if world > 1 and not args.no_sp_check:
-            checks.append(sp_check(job2, dist))
-            if not checks[-1]["passed"]:
-                if rank == 0:
-                    print(json.dumps({"metric": METRIC, "n_gpus": world, "error": "sequence-parallel output "
-                                      "differs from the single-GPU block", "sp_check": checks[-1]}))
-                dist.destroy_process_group()
-                sys.exit(2)
+        job2 = checked_job(pkg, params, SMALL_TOKENS, world, rank, dev, args, dist, checks)
         x2 = job2.shard(job2.full_input(1235))
         step2 = lambda: job2.block.forward(x2, job2.cos, job2.sin)
         for _ in range(max(3, args.warmup)):
