@@ -453,9 +453,11 @@ def kernel_row(label, entry, ms, bound, work, pk):
 
 
 def standalone_rows(pkg, tokens, dev, pk):
-    """The two named memory-bound operators that the block only runs fused (mod-scale-shift
-    inside LayerNorm, the quantizer of a plain bf16 tensor), timed alone on rotating buffers
-    larger than L2."""
+    """The memory-bound operators timed ALONE on rotating buffers larger than L2: the two that
+    the block only runs fused (mod-scale-shift inside LayerNorm, the quantizer of a plain bf16
+    tensor), and the two producer fusions (LayerNorm + modulation + quantizer, swiglu-quant),
+    whose in-block rows above are taken right after attention has pulled the SM clock down
+    under the power cap (both are instruction-issue-bound, so they follow the clock)."""
     import torch
     ops = pkg.ops
     g = torch.Generator(device=dev).manual_seed(3)
@@ -464,16 +466,28 @@ def standalone_rows(pkg, tokens, dev, pk):
     sc = (torch.randn((HIDDEN,), device=dev, generator=g) * 0.1).to(torch.bfloat16)
     sh = (torch.randn((HIDDEN,), device=dev, generator=g) * 0.1).to(torch.bfloat16)
     rows = []
-    for label, fn in (("mod_scale_shift (standalone)", lambda i: ops.mod_scale_shift_(xs[i % n_buf], sc, sh)),
-                      ("quantize_int8_rowwise (standalone)", lambda i: ops.quantize_int8_rowwise(xs[i % n_buf]))):
+
+    def timed(label, shape, fn):
         for i in range(3):
             fn(i)
         with ops.LaunchTimer() as timer:
             for i in range(11):
                 fn(i)
         recs = timer.results()
-        rows.append(kernel_row(f"{label} {tokens}x{HIDDEN}", recs[0]["name"],
+        rows.append(kernel_row(f"{label} {shape}", recs[0]["name"],
                                statistics.median(r["ms"] for r in recs), recs[0]["bound"], recs[0]["work"], pk))
+
+    timed("mod_scale_shift (standalone)", f"{tokens}x{HIDDEN}", lambda i: ops.mod_scale_shift_(xs[i % n_buf], sc, sh))
+    timed("quantize_int8_rowwise (standalone)", f"{tokens}x{HIDDEN}", lambda i: ops.quantize_int8_rowwise(xs[i % n_buf]))
+    timed("layernorm_mod_quant (standalone)", f"{tokens}x{HIDDEN}",
+          lambda i: ops.layernorm_mod_quant(xs[i % n_buf], sc, sh))
+    del xs
+    torch.cuda.empty_cache()
+    wide = [torch.randn((tokens, 2 * FFN), device=dev, generator=g).to(torch.bfloat16) for _ in range(2)]
+    timed("swiglu_quantize_int8_rowwise (standalone)", f"{tokens}x{2 * FFN}",
+          lambda i: ops.swiglu_quantize_int8_rowwise(wide[i % 2]))
+    del wide
+    torch.cuda.empty_cache()
     return rows
 
 
