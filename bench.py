@@ -64,6 +64,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-residual", action="store_true",
                     help="gated residuals as their own kernel instead of in the GEMM epilogue")
+    ap.add_argument("--no-fuse-swiglu", action="store_true",
+                    help="fc1 and swiglu-quant as the reference's two operators instead of SwiGLU in fc1's epilogue")
     ap.add_argument("--no-graph", action="store_true", help="single GPU: launch the kernels one by one")
     ap.add_argument("--no-sp-check", action="store_true", help="skip the 1-GPU-vs-N-GPU parity gate")
     ap.add_argument("--exchange", default="peer", choices=["peer", "all_to_all"],
@@ -258,7 +260,8 @@ def workload_config(tokens):
 class Job:
     """One rank's view of the block at a token count: shard bounds, block, rotary tables."""
 
-    def __init__(self, pkg, params, tokens, world, rank, dev, head_chunks, fuse_residual, exchange="all_to_all"):
+    def __init__(self, pkg, params, tokens, world, rank, dev, head_chunks, fuse_residual, exchange="all_to_all",
+                 fuse_swiglu=True):
         self.pkg, self.tokens, self.world, self.rank, self.dev = pkg, tokens, world, rank, dev
         self.exchange, self.exchange_note = ("all_to_all" if world > 1 else None), None
         self.splits = pkg.ulysses.sequence_splits(tokens, world)
@@ -281,7 +284,7 @@ class Job:
         self.chunks = chunks
         self.params = params
         self.block = pkg.block.DiTBlock(params, sp=self.sp, head_chunks=chunks, overlap=True,
-                                        fuse_residual=fuse_residual)
+                                        fuse_residual=fuse_residual, fuse_swiglu=fuse_swiglu)
         cos_all, sin_all = pkg.block.rope_tables(pkg.block.grid_positions(tokens))
         self.cos_all, self.sin_all = cos_all.to(dev), sin_all.to(dev)
         self.cos = self.cos_all[self.row0:self.row0 + self.L].contiguous()
@@ -320,7 +323,8 @@ def sp_check(job: Job, dist) -> dict:
     pkg, dev, T = job.pkg, job.dev, job.tokens
     x_full = job.full_input(4321)
     taps1, taps2 = {}, {}
-    single = pkg.block.DiTBlock(job.params, fuse_residual=job.block.fuse_residual)
+    single = pkg.block.DiTBlock(job.params, fuse_residual=job.block.fuse_residual,
+                                fuse_swiglu=job.block.fuse_swiglu)
     y1 = single.forward(x_full, job.cos_all, job.sin_all, taps=taps1)
     y2 = job.block.forward(job.shard(x_full), job.cos, job.sin, taps=taps2)
     torch.cuda.synchronize()
@@ -422,6 +426,9 @@ def kernel_table(pkg, block, x, cos, sin, pk, passes=3):
               "int8_gemm_dequant_residual out 3072->3072", "layernorm_mod_quant (adaLN 2)",
               "int8_gemm_dequant fc1 3072->16384", "swiglu_quantize_int8_rowwise",
               "int8_gemm_dequant_residual fc2 8192->3072"]
+    if getattr(block, "fuse_swiglu", False):
+        labels[7:9] = ["int8_gemm_dequant_swiglu fc1 3072->16384 (SwiGLU in the epilogue)",
+                       "quantize_int8_rowwise (SwiGLU product, 8192 wide)"]
     rows = []
     for i in range(per):
         ms = statistics.median(recs[p * per + i]["ms"] for p in range(passes))
@@ -495,7 +502,8 @@ def checked_job(pkg, params, tokens, world, rank, dev, args, dist, checks):
     """A Job at `tokens` that has passed the parity gate (N > 1), or exit 2.  If the peer
     exchange fails the gate, that is recorded in `exchange_note` (and in the failed check kept
     beside it) and the job is rebuilt on all-to-all collectives, which must then pass."""
-    job = Job(pkg, params, tokens, world, rank, dev, args.head_chunks, not args.no_fuse_residual, args.exchange)
+    job = Job(pkg, params, tokens, world, rank, dev, args.head_chunks, not args.no_fuse_residual, args.exchange,
+              not args.no_fuse_swiglu)
     if world == 1 or args.no_sp_check:
         return job
     check = sp_check(job, dist)
@@ -503,7 +511,8 @@ def checked_job(pkg, params, tokens, world, rank, dev, args, dist, checks):
     if not check["passed"] and job.exchange == "peer":
         failed = check
         job.close()
-        job = Job(pkg, params, tokens, world, rank, dev, args.head_chunks, not args.no_fuse_residual, "all_to_all")
+        job = Job(pkg, params, tokens, world, rank, dev, args.head_chunks, not args.no_fuse_residual, "all_to_all",
+                  not args.no_fuse_swiglu)
         job.exchange_note = "the peer exchange FAILED the parity gate; timed with all-to-all collectives instead"
         check = sp_check(job, dist)
         check["failed_peer_check"] = failed

@@ -34,6 +34,7 @@ SYMBOLS = {
     "b2_int8_gemm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b2_int8_gemm_dequant": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
     "b2_int8_gemm_dequant_residual": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b2_int8_gemm_dequant_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
     "b2_int8_linear": (_int, [_vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b2_int8_linear_noalloc": (_int, [_vp, _int, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
     "b2_flash_fwd": (_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 9 + [_f32, _vp]),

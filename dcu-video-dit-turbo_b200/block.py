@@ -2,7 +2,9 @@
 
 adaLN modulation -> INT8 QKV GEMM -> per-head QK RMSNorm + 3-D RoPE -> bf16 flash
 attention -> INT8 out-proj -> gated residual -> adaLN -> SwiGLU FFN (INT8 fc1,
-swiglu-quant, INT8 fc2) -> gated residual, on a token shard [L, C].
+swiglu-quant, INT8 fc2) -> gated residual, on a token shard [L, C].  By default swiglu-quant
+is split across the two kernels around it (SwiGLU in fc1's epilogue, the quantizer as its own
+pass over the half-width product); `fuse_swiglu=False` runs the reference's operator sequence.
 
 The reference project has no source for the block itself (it lives in the host
 application's model file); only its operator set comes from the reference.  The
@@ -71,9 +73,15 @@ def grid_positions(tokens: int, height: int = 22, width: int = 38) -> torch.Tens
 
 class DiTBlock:
     def __init__(self, params: dict, sp: UlyssesSP | None = None, head_chunks: int = 1,
-                 overlap: bool = True, fuse_residual: bool = True):
+                 overlap: bool = True, fuse_residual: bool = True, fuse_swiglu: bool = True):
         self.p = params
         self.fuse_residual = fuse_residual   # gated residual in the GEMM epilogue where it pays (same bits either way)
+        # SwiGLU in fc1's epilogue (same bits either way): the [L, 2*ffn] projection never reaches
+        # memory; needs fc1's rows interleaved gate/up in groups of 64, prepared once here
+        self.fuse_swiglu = bool(fuse_swiglu) and params["ffn"] % ops.SWIGLU_GROUP == 0
+        self._fc1_interleaved = None
+        if self.fuse_swiglu:
+            self._fc1_interleaved = tuple(ops.interleave_gate_up(params[k]) for k in ("wq_fc1", "ws_fc1", "b_fc1"))
         self.sp = sp
         self.head_chunks = head_chunks
         self.overlap = overlap
@@ -140,8 +148,12 @@ class DiTBlock:
             q8, s = ops.quantize_int8_rowwise(attn_rows)
         self._linear_residual(x, p["gate1"], q8, s, p["wq_out"], p["ws_out"], p["b_out"])
         q8, s = ops.layernorm_mod_quant(x, p["scale2"], p["shift2"])
-        f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])
-        q8, s = ops.swiglu_quantize_int8_rowwise(f)
+        if self.fuse_swiglu:
+            h = ops.int8_gemm_dequant_swiglu(q8, s.view(-1), *self._fc1_interleaved)
+            q8, s = ops.quantize_int8_rowwise(h)
+        else:
+            f = ops.int8_gemm_dequant(q8, s.view(-1), p["wq_fc1"], p["ws_fc1"], p["b_fc1"])
+            q8, s = ops.swiglu_quantize_int8_rowwise(f)
         self._linear_residual(x, p["gate2"], q8, s, p["wq_fc2"], p["ws_fc2"], p["b_fc2"])
         return x
 

@@ -292,6 +292,20 @@ int b2_int8_gemm_dequant_residual(const int8_t* A, const float* rs, const int8_t
   return launch_int8_gemm(A, W, nullptr, nullptr, rs, cs, bias, bias_kind, gate, x_inout, M, N, K, (cudaStream_t)stream);
 }
 
+int b2_int8_gemm_dequant_swiglu(const int8_t* A, const float* rs, const int8_t* W, const float* cs,
+                                const void* bias, int bias_kind, void* out, int64_t M, int64_t N,
+                                int64_t K, void* stream) {
+  if (bias_kind < B2_BIAS_NONE || bias_kind > B2_BIAS_FP32) return fail(B2_BAD_DTYPE, "int8_gemm_dequant_swiglu: bias must be none, bfloat16, or float32");
+  int st = check_gemm("int8_gemm_dequant_swiglu", A, W, M, N, K, 8);
+  if (st >= 0) return st;
+  if (N % 128 != 0)
+    return fail(B2_NOT_WHITELISTED, "int8_gemm_dequant_swiglu: N=%lld must be a multiple of 128 (gate and up rows interleaved in groups of 64)", (long long)N);
+  if (!rs || !cs || !out) return fail(B2_NULL_POINTER, "int8_gemm_dequant_swiglu: null pointer");
+  if (bias_kind != B2_BIAS_NONE && !bias) return fail(B2_NULL_POINTER, "int8_gemm_dequant_swiglu: bias kind %d with a null bias", bias_kind);
+  if (!aligned16(out)) return fail(B2_BAD_STRIDE, "int8_gemm_dequant_swiglu: out must be 16-byte aligned");
+  return launch_int8_gemm(A, W, nullptr, out, rs, cs, bias, bias_kind, nullptr, nullptr, M, N, K, (cudaStream_t)stream, 1);
+}
+
 int b2_int8_linear(const void* x, int input_act, const int8_t* W, const float* cs, const void* bias,
                    int bias_kind, void* out, int8_t* q_scratch, float* s_scratch, int64_t M,
                    int64_t N, int64_t K, void* stream) {

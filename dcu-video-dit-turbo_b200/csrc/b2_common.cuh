@@ -115,6 +115,19 @@ __device__ __forceinline__ uint32_t bf16x2_add_rn(uint32_t a, uint32_t b) {
   asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
+// SiLU in fp32 exactly as the eager op computes it: g / (1 + expf(-g)) with the accurate
+// expf and an IEEE division.
+__device__ __forceinline__ float silu_exact(float g) {
+  return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+}
+// bf16( bf16(silu(g)) * u ) on a packed pair from the exact formula
+// (kernels/swiglu-quant/swiglu_quant_kernel.hip:18-27 in the reference: two roundings).
+__device__ __forceinline__ uint32_t swiglu_pair_exact(uint32_t g, uint32_t u) {
+  const uint32_t s = pack_bf16x2_rn(silu_exact(bf16lo_to_f32(g)), silu_exact(bf16hi_to_f32(g)));
+  // second rounding: the fp32 product of two bf16 values is exact, so rounding it to bf16 is
+  // the packed bf16 multiply's single rounding
+  return bf16x2_mul_rn(s, u);
+}
 __device__ __forceinline__ float round_bf16_f32(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }

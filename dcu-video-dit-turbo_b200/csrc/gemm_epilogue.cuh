@@ -7,6 +7,13 @@
 //   residual   x[row, col] = bf16( x + bf16(gate[col] * y) ) in place: the gated residual
 //              of the DiT block applied while the tile is still in registers, so y never
 //              makes a round trip through memory
+//   swiglu     the weight rows (with their scales and bias) arrive interleaved in groups of
+//              64: accumulator columns [128k, 128k+64) are gate columns [64k, 64k+64) and
+//              [128k+64, 128k+128) the matching up columns; out[row, 64k+j] =
+//              bf16( bf16(silu(y_gate)) * y_up ), y as in dequant: the first half of
+//              swiglu-quant (kernels/swiglu-quant/swiglu_quant_kernel.hip:18-27 in the
+//              reference) applied while the tile is in registers, so the [M, 2F] projection
+//              never reaches memory; out is bf16 [M, N/2]
 #pragma once
 
 #include "b2_common.cuh"
@@ -23,6 +30,8 @@ struct EpilogueArgs {
   int bias_kind;
   const __nv_bfloat16* gate;   // residual mode when non-null (with `residual`)
   __nv_bfloat16* residual;
+  int swiglu;                  // swiglu mode (dequant mode's pointers; out_bf16 is [M, N/2])
+  const uint16_t* silu_lut;    // swiglu mode: bf16(silu(g)) indexed by the gate's 16 bits (global memory)
 };
 
 constexpr int kEpiTileN = 256;
@@ -96,6 +105,39 @@ __device__ __forceinline__ void epilogue_compute_chunk(const EpilogueArgs& a, co
       }
       o[j] = in ? p : 0u;
     }
+  }
+}
+
+// Dequant + bias of a packed pair of accumulators (the dequant mode's arithmetic).
+__device__ __forceinline__ uint32_t epilogue_dequant_pair(uint32_t v0, uint32_t v1, float rsv, float cs0,
+                                                          float cs1, bool has_bias, float b0, float b1) {
+  const float f0 = __fmul_rn(__int2float_rn((int)v0), __fmul_rn(rsv, cs0));
+  const float f1 = __fmul_rn(__int2float_rn((int)v1), __fmul_rn(rsv, cs1));
+  uint32_t p = pack_bf16x2_rn(f0, f1);
+  if (has_bias) p = pack_bf16x2_rn(__fadd_rn(bf16lo_to_f32(p), b0), __fadd_rn(bf16hi_to_f32(p), b1));
+  return p;
+}
+
+// swiglu mode: 32 gate accumulators (tile offset cg) and the 32 matching up accumulators
+// (tile offset cu = cg + 64) of one row -> 16 packed bf16 outputs.
+__device__ __forceinline__ void epilogue_swiglu_chunk(const EpilogueArgs& a, const uint32_t (&vg)[32],
+                                                      const uint32_t (&vu)[32], int cg, int cu, float rsv,
+                                                      const float* cvec, uint32_t (&o)[16]) {
+  const bool has_bias = a.bias_kind != B2_BIAS_NONE;
+  const float* gs = cvec + cg;
+  const float* gb = cvec + kEpiTileN + cg;
+  const float* us = cvec + cu;
+  const float* ub = cvec + kEpiTileN + cu;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint32_t g = epilogue_dequant_pair(vg[2 * j], vg[2 * j + 1], rsv, gs[2 * j], gs[2 * j + 1], has_bias,
+                                             gb[2 * j], gb[2 * j + 1]);
+    const uint32_t u = epilogue_dequant_pair(vu[2 * j], vu[2 * j + 1], rsv, us[2 * j], us[2 * j + 1], has_bias,
+                                             ub[2 * j], ub[2 * j + 1]);
+    // bf16(silu(g)) is a function of the gate's 16 bits: two cached table loads replace two
+    // expf + two IEEE divisions per pair, which a single warp per scheduler cannot hide
+    const uint32_t sl = (uint32_t)__ldg(a.silu_lut + (g & 0xffffu)) | ((uint32_t)__ldg(a.silu_lut + (g >> 16)) << 16);
+    o[j] = bf16x2_mul_rn(sl, u);
   }
 }
 

@@ -201,12 +201,33 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = row < epi.M;
       const float rsv = (fused && row_ok) ? epi.rs[row] : 0.f;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      if (fused && epi.swiglu) {
+        // 64 gate + 64 up accumulator columns -> 64 outputs, stored directly
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c, v);
-        tmem_wait_ld();
-        if (row_ok && col0 + c < epi.N) epilogue_store_chunk(epi, v, row, col0 + c, c, rsv, cvec);
+        for (int c = 0; c < BN; c += 128) {
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t vg[32], vu[32];
+            uint32_t o[16];
+            tmem_ld_32x32b_x32(taddr + c + 32 * hh, vg);
+            tmem_ld_32x32b_x32(taddr + c + 64 + 32 * hh, vu);
+            tmem_wait_ld();
+            if (row_ok && col0 + c < epi.N) {
+              epilogue_swiglu_chunk(epi, vg, vu, c + 32 * hh, c + 64 + 32 * hh, rsv, cvec, o);
+              uint4* dst = reinterpret_cast<uint4*>(epi.out_bf16 + (int64_t)row * (epi.N / 2) + (col0 + c) / 2 + 32 * hh);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c, v);
+          tmem_wait_ld();
+          if (row_ok && col0 + c < epi.N) epilogue_store_chunk(epi, v, row, col0 + c, c, rsv, cvec);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -251,9 +272,9 @@ int encode_k_major_map(CUtensorMap* map, const void* base, int64_t rows, int64_t
 int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
                      const float* rs, const float* cs, const void* bias, int bias_kind,
                      const void* gate, void* residual, int64_t M, int64_t N, int64_t K,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, int swiglu) {
   // large M: two CTAs per 256x256 tile (less operand traffic per SM); else one CTA per tile
-  const int pair_status = launch_int8_gemm_pair(A, W, out_i32, out_bf16, rs, cs, bias, bias_kind, gate, residual, M, N, K, stream);
+  const int pair_status = launch_int8_gemm_pair(A, W, out_i32, out_bf16, rs, cs, bias, bias_kind, gate, residual, M, N, K, stream, swiglu);
   if (pair_status >= 0) return pair_status;
   static PerDeviceSetup per_device;
   const DeviceSlot* slot = nullptr;
@@ -266,6 +287,11 @@ int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* o
     return B2_OK;
   }, &slot);
   if (setup_status != B2_OK) return setup_status;
+  const uint16_t* silu_lut = nullptr;
+  if (swiglu) {
+    const int lut_status = silu_table_device_pointer(stream, &silu_lut);
+    if (lut_status != B2_OK) return lut_status;
+  }
   CUtensorMap ta, tb;
   int st = encode_k_major_map(&ta, A, M, K, BM);
   if (st != B2_OK) return st;
@@ -292,6 +318,8 @@ int launch_int8_gemm(const int8_t* A, const int8_t* W, int32_t* out_i32, void* o
   a.epi.bias_kind = bias_kind;
   a.epi.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
   a.epi.residual = reinterpret_cast<__nv_bfloat16*>(residual);
+  a.epi.swiglu = swiglu;
+  a.epi.silu_lut = silu_lut;
 
   const int sms = slot->a;
   const int grid = a.num_tiles < sms ? a.num_tiles : sms;

@@ -253,7 +253,34 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = row < epi.M;
       const float rsv = (fused && row_ok) ? epi.rs[row] : 0.f;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
-      if (fused) {
+      if (fused && epi.swiglu) {
+        // 128 accumulator columns (64 gate + 64 up) per step -> 64 output columns, staged and
+        // stored like the dequant mode's 64-column step, at half the column offset
+        const uint32_t stage = ring + SMEM_RING + quarter * kEpiStageBytes;
+        const int row_warp = row - lane;   // global row of lane 0
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 128) {
+          if (col0 + c >= epi.N) break;
+          if (lane == 0) bulk_wait_group_read<0>();   // the previous store has read the tile
+          __syncwarp();
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t vg[32], vu[32];
+            uint32_t o[16];
+            tmem_ld_32x32b_x32(taddr + c + 32 * hh, vg);
+            tmem_ld_32x32b_x32(taddr + c + 64 + 32 * hh, vu);
+            tmem_wait_ld();
+            epilogue_swiglu_chunk(epi, vg, vu, c + 32 * hh, c + 64 + 32 * hh, rsv, cvec, o);
+            epilogue_stage_write(stage, lane, hh, o);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row_warp < epi.M) {
+            tma_store_2d(&tmap_out, stage, (col0 + c) / 2, row_warp);
+            bulk_commit_group();
+          }
+        }
+      } else if (fused) {
         // 64 columns per step: two 32-column halves are computed into the warp's staging tile,
         // then one lane issues the TMA store of the 32 x 64 tile
         const uint32_t stage = ring + SMEM_RING + quarter * kEpiStageBytes;
@@ -353,7 +380,7 @@ int encode_out_map(CUtensorMap* map, void* base, int64_t M, int64_t N) {
 int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, void* out_bf16,
                           const float* rs, const float* cs, const void* bias, int bias_kind,
                           const void* gate, void* residual, int64_t M, int64_t N, int64_t K,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, int swiglu) {
   // slot.a = 1 when the pair kernel can run on this device, slot.b = resident clusters
   static PerDeviceSetup per_device;
   const DeviceSlot* slot = nullptr;
@@ -392,6 +419,11 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
   if (setup_status != B2_OK) return setup_status;
   const int enabled = slot->a, max_clusters = slot->b;
   if (!enabled || M < 2 * BM) return -1;
+  const uint16_t* silu_lut = nullptr;
+  if (swiglu) {
+    const int lut_status = silu_table_device_pointer(stream, &silu_lut);
+    if (lut_status != B2_OK) return lut_status;
+  }
 
   CUtensorMap ta, tb, tout;
   int st = encode_map(&ta, A, M, K, BM);
@@ -401,7 +433,7 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
   // fused modes store through this map (the plain int32 mode stores directly and never uses it)
   void* bf16_dst = residual != nullptr ? residual : out_bf16;
   if (bf16_dst != nullptr) {
-    st = encode_out_map(&tout, bf16_dst, M, N);
+    st = encode_out_map(&tout, bf16_dst, M, swiglu ? N / 2 : N);
     if (st != B2_OK) return st;
   } else {
     tout = ta;
@@ -426,6 +458,8 @@ int launch_int8_gemm_pair(const int8_t* A, const int8_t* W, int32_t* out_i32, vo
   a.epi.bias_kind = bias_kind;
   a.epi.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
   a.epi.residual = reinterpret_cast<__nv_bfloat16*>(residual);
+  a.epi.swiglu = swiglu;
+  a.epi.silu_lut = silu_lut;
   const int clusters = a.num_tiles < max_clusters ? a.num_tiles : max_clusters;
   int8_gemm_2cta_kernel<<<clusters * 2, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, tout, a);
   return check_launch("int8_gemm (CTA pair)");

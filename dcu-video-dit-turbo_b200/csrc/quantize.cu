@@ -138,12 +138,6 @@ __global__ void fill_f32_kernel(float* p, int64_t n, float v) {
 
 // ---- SwiGLU + quantizer ------------------------------------------------------
 
-// SiLU in fp32 exactly as the eager op computes it: g / (1 + expf(-g)) with the accurate
-// expf and an IEEE division.
-__device__ __forceinline__ float silu_exact(float g) {
-  return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
-}
-
 // bf16(silu(g)) depends on the 16 bits of the bf16 gate alone, so the whole function is a
 // table of 65536 bf16 values (128 KB).  It is built once per device from the exact formula
 // above and every CTA of the row kernel keeps a copy in shared memory: the first rounding of
@@ -159,13 +153,7 @@ __global__ void build_silu_table_kernel() {
     g_silu_bf16[i] = __bfloat16_as_ushort(__float2bfloat16_rn(silu_exact(__uint_as_float(i << 16))));
 }
 
-// bf16( bf16(silu(g)) * u ) on a packed pair from the exact formula (generic kernel).
-__device__ __forceinline__ uint32_t swiglu_pair_exact(uint32_t g, uint32_t u) {
-  const uint32_t s = pack_bf16x2_rn(silu_exact(bf16lo_to_f32(g)), silu_exact(bf16hi_to_f32(g)));
-  // second rounding: the fp32 product of two bf16 values is exact, so rounding it to bf16 is
-  // the packed bf16 multiply's single rounding
-  return bf16x2_mul_rn(s, u);
-}
+// swiglu_pair_exact (b2_common.cuh) is the same from the exact formula (generic kernel).
 // The same through the table in shared memory.
 __device__ __forceinline__ uint32_t swiglu_pair_lut(uint32_t g, uint32_t u, const uint16_t* lut) {
   const uint32_t s = (uint32_t)lut[g & 0xffffu] | ((uint32_t)lut[g >> 16] << 16);
@@ -369,6 +357,19 @@ int launch_swiglu_rows(const void* x, int8_t* q, float* scale, int64_t M, int kv
 }
 
 }  // namespace
+
+// The device address of the table on the current device (built first if need be), for
+// kernels of other translation units that look SiLU up in global memory.
+int silu_table_device_pointer(cudaStream_t stream, const uint16_t** table) {
+  const int st = ensure_silu_table(stream);
+  if (st != B2_OK) return st;
+  void* p = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&p, g_silu_bf16);
+  if (e != cudaSuccess) return fail(B2_LAUNCH_FAILED, "SiLU table address: %s", cudaGetErrorString(e));
+  *table = reinterpret_cast<const uint16_t*>(p);
+  return B2_OK;
+}
+
 
 int launch_swiglu_quantize(const void* x, int8_t* q, float* scale, int64_t M, int64_t K,
                            cudaStream_t stream) {

@@ -294,6 +294,53 @@ def int8_gemm_dequant_residual_(x: torch.Tensor, gate: torch.Tensor, a: torch.Te
     return x
 
 
+SWIGLU_GROUP = 64   # gate / up rows alternate in groups of this many in an interleaved projection
+
+
+def interleave_gate_up(t: torch.Tensor, group: int = SWIGLU_GROUP) -> torch.Tensor:
+    """Reorder the leading dimension of a SwiGLU projection's weight [2F, K], column scale [2F]
+    or bias [2F] from (all gate rows, all up rows) to groups of `group` gate rows followed by
+    the matching `group` up rows: the layout int8_gemm_dequant_swiglu reads.  Done once when
+    the weights are loaded."""
+    two_f = t.shape[0]
+    _require(two_f % (2 * group) == 0, f"leading dimension must be a multiple of {2 * group}")
+    f = two_f // 2
+    gate, up = t[:f], t[f:]
+    rest = tuple(t.shape[1:])
+    return torch.stack((gate.reshape(f // group, group, *rest), up.reshape(f // group, group, *rest)),
+                       dim=1).reshape(two_f, *rest).contiguous()
+
+
+def int8_gemm_dequant_swiglu(a: torch.Tensor, row_scale: torch.Tensor, w_interleaved: torch.Tensor,
+                             col_scale_interleaved: torch.Tensor,
+                             bias_interleaved: torch.Tensor | None) -> torch.Tensor:
+    """The FFN's first projection with SwiGLU in the GEMM's epilogue: returns
+    bf16 [M, F] = bf16(bf16(silu(gate)) * up) of the dequantised projection, the operands
+    interleaved by `interleave_gate_up`.  quantize_int8_rowwise of the result equals
+    swiglu_quantize_int8_rowwise of the plain projection bit for bit."""
+    _require(a.is_cuda and a.dtype == torch.int8 and w_interleaved.dtype == torch.int8 and a.is_contiguous()
+             and w_interleaved.is_contiguous() and a.dim() == 2 and w_interleaved.dim() == 2
+             and a.shape[1] == w_interleaved.shape[1],
+             "a int8 [M,K] and w int8 [2F,K] must be contiguous CUDA tensors")
+    m, k = a.shape
+    n = w_interleaved.shape[0]
+    _require(n % (2 * SWIGLU_GROUP) == 0, f"the projection width must be a multiple of {2 * SWIGLU_GROUP}")
+    _require(w_interleaved.is_cuda and w_interleaved.device == a.device
+             and row_scale.is_cuda and row_scale.device == a.device
+             and col_scale_interleaved.is_cuda and col_scale_interleaved.device == a.device,
+             "all inputs must be on the same device")
+    _require(row_scale.dtype == torch.float32 and col_scale_interleaved.dtype == torch.float32
+             and row_scale.numel() == m and col_scale_interleaved.numel() == n
+             and row_scale.is_contiguous() and col_scale_interleaved.is_contiguous(), "scale mismatch")
+    kind = _bias_kind(bias_interleaved, n, a.device)
+    out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=a.device)
+    if m and n:
+        _call("b2_int8_gemm_dequant_swiglu", a, a.data_ptr(), row_scale.data_ptr(), w_interleaved.data_ptr(),
+              col_scale_interleaved.data_ptr(), _ptr(bias_interleaved) if kind else None, kind,
+              out.data_ptr(), m, n, k, _stream(a), work=("int8", 2 * m * n * k))
+    return out
+
+
 def int8_linear(x: torch.Tensor, w: torch.Tensor, col_scale: torch.Tensor,
                 bias: torch.Tensor | None = None, input_act: str | None = None,
                 scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:

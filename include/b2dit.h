@@ -122,6 +122,22 @@ int b2_int8_gemm_dequant_residual(const int8_t* A, const float* row_scale, const
                                   const void* gate_bf16, void* x_inout_bf16, int64_t M, int64_t N,
                                   int64_t K, void* stream);
 
+/* The same GEMM with the first half of swiglu-quant applied in the epilogue (for the FFN's
+ * first projection).  W int8 [N,K], col_scale fp32 [N] and bias [N] hold the projection's gate
+ * rows and up rows INTERLEAVED in groups of 64: rows [128k, 128k+64) are gate rows
+ * [64k, 64k+64) and rows [128k+64, 128k+128) the matching up rows (N = 2F, N % 128 == 0).
+ *   out bf16 [M, N/2]:  out[m, 64k+j] = bf16( bf16(silu(y_gate)) * y_up ),
+ * y the dequantised, biased bf16 values above, silu(g) = g / (1 + expf(-g)) in fp32: exactly
+ * what kernels/swiglu-quant/swiglu_quant_kernel.hip:18-27 computes from the [M,2F] projection
+ * before it quantises, so b2_quantize_int8_rowwise(out) gives the bits of
+ * b2_swiglu_quantize_int8_rowwise(b2_int8_gemm_dequant(...)) with the un-interleaved weight,
+ * and the [M,2F] tensor never goes through memory.  (A fusion; the reference runs the
+ * projection and swiglu-quant as two operators.) */
+int b2_int8_gemm_dequant_swiglu(const int8_t* A, const float* row_scale, const int8_t* W_interleaved,
+                                const float* col_scale_interleaved, const void* bias_interleaved,
+                                int bias_kind, void* out_bf16, int64_t M, int64_t N, int64_t K,
+                                void* stream);
+
 /* Whole INT8 linear: (activation) -> rowwise quantise -> GEMM -> dequant epilogue.
  * Replaces _int8_linear_nocopy, launcher/benchmark_launcher_v14_hires_int8_candidate.py:960-1067
  * (bf16 output, per-output-channel weight scale, no ConvRot).

@@ -355,3 +355,54 @@ def test_linear_dispatch_routes_quantized_weights_to_the_int8_path(cuda_pkg, ref
     torch.nn.functional.linear(torch.randn((3, 64), generator=g).to(torch.bfloat16).to(DEV), odd)
     assert d.summary()["fallbacks"] == {"disabled": 1, "weight_shape_or_arch": 1}
     pkg.ops.check_device_status()
+
+
+@pytest.mark.parametrize("m,f,k", [(1, 64, 16), (100, 128, 144), (255, 192, 512), (256, 64, 128), (300, 576, 272),
+                                   (513, 1024, 3072), (1000, 8192, 3072), (4099, 8192, 3072)])
+@pytest.mark.parametrize("bias_kind", ["bf16", "fp32", None])
+def test_gemm_with_swiglu_in_the_epilogue_equals_projection_then_swiglu_quant(cuda_pkg, ref, m, f, k, bias_kind):
+    """SwiGLU moved into the first FFN projection's epilogue (weights interleaved gate/up in
+    groups of 64) followed by the plain quantizer must give exactly the bits of the reference's
+    operator sequence: projection [M, 2F] -> swiglu_quantize_int8_rowwise.  Covers the
+    single-CTA kernel (M < 256), the CTA-pair kernel, ragged M, several tiles per row and all
+    bias kinds; the product itself is also compared with eager SwiGLU on the device."""
+    ops = cuda_pkg.ops
+    g = torch.Generator().manual_seed(m * 7 + f + k)
+    a = _rand_i8((m, k), g)
+    w = _rand_i8((2 * f, k), g)
+    rs = (torch.rand((m,), generator=g) * 0.02 + 1e-3).float()
+    cs = (torch.rand((2 * f,), generator=g) * 2e-3 + 1e-4).float()
+    bias = None
+    if bias_kind == "bf16":
+        bias = (torch.randn((2 * f,), generator=g) * 0.5).to(torch.bfloat16)
+    elif bias_kind == "fp32":
+        bias = (torch.randn((2 * f,), generator=g) * 0.5).float()
+    ad, wd, rsd, csd = a.to(DEV), w.to(DEV), rs.to(DEV), cs.to(DEV)
+    bd = None if bias is None else bias.to(DEV)
+    # the reference's sequence
+    proj = ops.int8_gemm_dequant(ad, rsd, wd, csd, bd)                      # bf16 [M, 2F]
+    q_want, s_want = ops.swiglu_quantize_int8_rowwise(proj)
+    # the fused form
+    il = ops.interleave_gate_up
+    h = ops.int8_gemm_dequant_swiglu(ad, rsd, il(wd), il(csd), None if bd is None else il(bd))
+    assert h.shape == (m, f) and h.dtype == torch.bfloat16
+    h_eager = torch.nn.functional.silu(proj[:, :f]) * proj[:, f:]      # ATen: silu in fp32 -> bf16, mul -> bf16
+    assert torch.equal(bits(h), bits(h_eager)), f"{(bits(h) != bits(h_eager)).sum().item()} products differ"
+    q, s = ops.quantize_int8_rowwise(h)
+    assert torch.equal(q, q_want) and torch.equal(bits(s), bits(s_want))
+    cuda_pkg.ops.check_device_status(torch.device(DEV))
+
+
+def test_interleave_gate_up_layout_and_refusals(cuda_pkg):
+    ops = cuda_pkg.ops
+    t = torch.arange(256).view(256, 1).repeat(1, 3)
+    il = ops.interleave_gate_up(t)
+    assert il.shape == t.shape
+    assert il[:64, 0].tolist() == list(range(0, 64)) and il[64:128, 0].tolist() == list(range(128, 192))
+    assert il[128:192, 0].tolist() == list(range(64, 128)) and il[192:, 0].tolist() == list(range(192, 256))
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        ops.interleave_gate_up(torch.zeros(192 + 8))
+    a = torch.zeros((4, 16), dtype=torch.int8, device=DEV)
+    w = torch.zeros((72, 16), dtype=torch.int8, device=DEV)
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        ops.int8_gemm_dequant_swiglu(a, torch.ones(4, device=DEV), w, torch.ones(72, device=DEV), None)
