@@ -131,8 +131,10 @@ int b2_int8_gemm_dequant_residual(const int8_t* A, const float* row_scale, const
  * what kernels/swiglu-quant/swiglu_quant_kernel.hip:18-27 computes from the [M,2F] projection
  * before it quantises, so b2_quantize_int8_rowwise(out) gives the bits of
  * b2_swiglu_quantize_int8_rowwise(b2_int8_gemm_dequant(...)) with the un-interleaved weight,
- * and the [M,2F] tensor never goes through memory.  (A fusion; the reference runs the
- * projection and swiglu-quant as two operators.) */
+ * and the [M,2F] tensor never goes through memory.  bf16(silu(g)) comes from the same
+ * 65536-entry table as b2_swiglu_quantize_int8_rowwise (built from that formula on the first
+ * call on a device, which waits for it: make that call before any stream capture).  (A
+ * fusion; the reference runs the projection and swiglu-quant as two operators.) */
 int b2_int8_gemm_dequant_swiglu(const int8_t* A, const float* row_scale, const int8_t* W_interleaved,
                                 const float* col_scale_interleaved, const void* bias_interleaved,
                                 int bias_kind, void* out_bf16, int64_t M, int64_t N, int64_t K,
