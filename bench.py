@@ -50,7 +50,7 @@ NVLINK_PEER_GBS = 770.0
 INT8_NOMINAL_TOPS = 4500.0     # dense INT8, nominal; no measured INT8 peak exists on this pool
 KERNEL_CHOICES = ["flash", "gemm_qkv", "gemm_fc1", "gemm_c1", "quant", "swiglu", "mod", "ln_quant",
                   "rope_pack", "quant_gathered", "gemm_out_residual", "gemm_fc2", "gemm_fc2_residual",
-                  "frames_u8", "epilogue", "gate", "rope"]
+                  "frames_u8", "epilogue", "gate", "rope", "gemm_fc1_swiglu"]
 
 
 def parse():
@@ -786,6 +786,12 @@ def run_kernel(args):
         rs, cs, b, gate = torch.rand(T, device=dev), torch.rand(n, device=dev) * 1e-4, vec(n), vec(n)
         xs = [rnd(T, n) for _ in range(nbuf(T * n * 2))]
         fn = lambda i: ops.int8_gemm_dequant_residual_(xs[i % len(xs)], gate, a, rs, w, cs, b)
+        work, unit, peak, bound = 2.0 * T * n * k, "TOP/s", 2 * pk["bf16_burst"], "tensor"
+    elif name == "gemm_fc1_swiglu":   # first FFN projection with SwiGLU in the epilogue (values random: timing only)
+        k, n = HIDDEN, 2 * FFN
+        a, w = ri8(T, k), ri8(n, k)
+        rs, cs, b = torch.rand(T, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-2, vec(n)
+        fn = lambda i: ops.int8_gemm_dequant_swiglu(a, rs, w, cs, b)
         work, unit, peak, bound = 2.0 * T * n * k, "TOP/s", 2 * pk["bf16_burst"], "tensor"
     elif name.startswith("gemm"):
         k, n = {"gemm_qkv": (HIDDEN, 3 * HIDDEN), "gemm_fc1": (HIDDEN, 2 * FFN), "gemm_c1": (HIDDEN, HIDDEN),
