@@ -69,25 +69,35 @@ __device__ __forceinline__ void epilogue_prefetch_residual(const EpilogueArgs& a
     if (col0 + b / 2 < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + b));
 }
 
+// Residual mode: the 32 columns of x that one chunk of one row updates, as four 16-byte loads
+// (8 columns each); groups at or beyond N, and rows at or beyond M, stay zero.  Issued one chunk
+// AHEAD of the arithmetic that needs them, so that the trip to L2 overlaps the current chunk.
+__device__ __forceinline__ void epilogue_load_residual(const EpilogueArgs& a, int row, int col, uint4 (&x)[4]) {
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) x[j4] = make_uint4(0, 0, 0, 0);
+  if (a.gate == nullptr || row >= a.M) return;
+  const uint4* xsrc = reinterpret_cast<const uint4*>(a.residual + (int64_t)row * a.N + col);
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4)
+    if (col + j4 * 8 < a.N) x[j4] = xsrc[j4];
+}
+
 // Dequant (+ bias, + gated residual) of one 32-column chunk of one row into 16 packed bf16
 // words.  `c` is the chunk's offset inside the tile, `col` its global column (< N).  In
-// residual mode x is read here (8 columns per 16-byte load); 8-column groups at or beyond N are
-// left as zeros (they are never stored).
+// residual mode `x` holds the chunk's residual columns (epilogue_load_residual); 8-column groups
+// at or beyond N are left as zeros (they are never stored).
 __device__ __forceinline__ void epilogue_compute_chunk(const EpilogueArgs& a, const uint32_t (&v)[32],
-                                                       int row, int col, int c, float rsv,
-                                                       const float* cvec, uint32_t (&o)[16]) {
+                                                       int col, int c, float rsv, const float* cvec,
+                                                       const uint4 (&x)[4], uint32_t (&o)[16]) {
   const float* cscale = cvec + c;
   const float* cbias = cvec + kEpiTileN + c;
   const float* cgate = cvec + 2 * kEpiTileN + c;
   const bool has_bias = a.bias_kind != B2_BIAS_NONE;
   const bool residual = a.gate != nullptr;
-  const uint4* xsrc = residual ? reinterpret_cast<const uint4*>(a.residual + (int64_t)row * a.N + col) : nullptr;
 #pragma unroll
   for (int j4 = 0; j4 < 4; ++j4) {  // N % 8 == 0: whole 8-column groups are in or out
-    uint4 xv = make_uint4(0, 0, 0, 0);
     const bool in = col + j4 * 8 < a.N;
-    if (residual && in && row < a.M) xv = xsrc[j4];
-    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    const uint32_t xw[4] = {x[j4].x, x[j4].y, x[j4].z, x[j4].w};
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       const int j = j4 * 4 + jj;

@@ -285,6 +285,8 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // then one lane issues the TMA store of the 32 x 64 tile
         const uint32_t stage = ring + SMEM_RING + quarter * kEpiStageBytes;
         const int row_warp = row - lane;   // global row of lane 0
+        uint4 x_next[4];   // residual mode: the next chunk's columns of x, loaded one chunk ahead
+        epilogue_load_residual(epi, row, col0, x_next);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 64) {
           if (col0 + c >= epi.N) break;
@@ -294,12 +296,17 @@ int8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int hh = 0; hh < 2; ++hh) {
             uint32_t v[32];
             uint32_t o[16];
+            uint4 x_now[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x_now[i] = x_next[i];
+            const int c_next = c + 32 * hh + 32;
+            if (c_next < BN) epilogue_load_residual(epi, row, col0 + c_next, x_next);
             tmem_ld_32x32b_x32(taddr + c + 32 * hh, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i] = 0u;
             if (col0 + c + 32 * hh < epi.N)
-              epilogue_compute_chunk(epi, v, row, col0 + c + 32 * hh, c + 32 * hh, rsv, cvec, o);
+              epilogue_compute_chunk(epi, v, col0 + c + 32 * hh, c + 32 * hh, rsv, cvec, x_now, o);
             epilogue_stage_write(stage, lane, hh, o);
           }
           fence_proxy_async_smem();
