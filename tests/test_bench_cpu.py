@@ -54,3 +54,21 @@ def test_kernel_row_rates():
     bf = b.kernel_row("f", "b2_f", 10.0, "bf16", 7_000_000_000_000, pk)      # 7e12 flop in 10 ms = 700 TFLOP/s
     assert abs(bf["achieved"] - 700.0) < 1e-6 and abs(bf["frac"] - 0.5) < 1e-9
     assert "achieved" not in b.kernel_row("x", "b2_x", 1.0, None, None, pk)
+    # kernels that store into peer GPUs are accounted against the measured peer-copy rate
+    nv = b.kernel_row("s", "b2_s", 0.1, "nvlink", 38_500_000, pk)            # 38.5 MB in 0.1 ms = 385 GB/s
+    assert nv["unit"] == "GB/s" and abs(nv["achieved"] - 385.0) < 1e-6 and abs(nv["frac"] - 0.5) < 1e-9
+    assert nv["peak"] == b.NVLINK_PEER_GBS
+
+
+def test_exchange_and_fusion_flags_parse():
+    b = _bench()
+    old = sys.argv
+    try:
+        sys.argv = ["bench.py"]
+        args = b.parse()
+        assert args.exchange == "peer" and not args.no_fuse_swiglu and not args.no_fuse_residual
+        sys.argv = ["bench.py", "--exchange", "all_to_all", "--no-fuse-swiglu", "--kernel", "gemm_fc1_swiglu"]
+        args = b.parse()
+        assert args.exchange == "all_to_all" and args.no_fuse_swiglu and args.kernel == "gemm_fc1_swiglu"
+    finally:
+        sys.argv = old

@@ -40,3 +40,22 @@ def test_push_plan_replayed_on_bytes_equals_the_reverse_all_to_all(pkg, ref, wor
 def test_peer_exchange_needs_a_cuda_device(pkg):
     with pytest.raises(RuntimeError, match="CUDA device memory"):
         pkg.peer.PeerBuffer(64, torch.device("cpu"))
+
+
+def test_interleave_gate_up_is_a_permutation_in_groups_of_64(pkg):
+    """Host-side weight preparation for the SwiGLU epilogue (pure tensor indexing, no kernel):
+    rows [128k, 128k+64) of the result are gate rows [64k, 64k+64), rows [128k+64, 128k+128) the
+    matching up rows, for weights, scales and biases alike."""
+    ops = pkg.ops
+    f = 192
+    w = torch.arange(2 * f * 5).view(2 * f, 5)
+    il = ops.interleave_gate_up(w)
+    assert il.shape == w.shape and il.is_contiguous()
+    for k in range(f // 64):
+        assert torch.equal(il[128 * k:128 * k + 64], w[64 * k:64 * k + 64])                  # gate rows
+        assert torch.equal(il[128 * k + 64:128 * k + 128], w[f + 64 * k:f + 64 * k + 64])    # up rows
+    v = torch.arange(2 * f)
+    assert torch.equal(ops.interleave_gate_up(v), ops.interleave_gate_up(v.view(-1, 1)).view(-1))
+    assert sorted(ops.interleave_gate_up(v).tolist()) == v.tolist()
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        ops.interleave_gate_up(torch.zeros(2 * 96))
