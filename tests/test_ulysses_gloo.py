@@ -1,5 +1,6 @@
 """Ulysses layout transforms on two CPU ranks (gloo): uneven token splits, the
-packed head-chunk all-to-all, and the agreement check of the overlap flag."""
+packed head-chunk all-to-all, the call order and layouts of the peer-store exchange (peer
+memory emulated by collectives), and the agreement check of the overlap flag."""
 import os
 import socket
 import sys
@@ -84,6 +85,62 @@ def _worker(rank, world, port, seq, heads, flag_mismatch, result_dir):
             assert tuple(result.shape) == (chunks, world, splits[rank], hl // chunks, D)
             assert torch.equal(ref.unpack_gathered(result), want.reshape(splits[rank], heads * D))
             assert torch.equal(sp.unpack_gathered(result), want.reshape(splits[rank], heads * D))
+        # the peer-store form of the exchange, with the peers' memory emulated by collectives: the
+        # "scatter kernel" delivers what pack + all-to-all delivers, the "push kernel" moves the
+        # byte ranges of peer.push_plan; attention_peer must order scatter, barrier, attention,
+        # push, barrier and return the gathered layout of the collective path
+        log = []
+
+        class EmulatedPeer:
+            def __init__(self):
+                self.recv = torch.zeros((1, sp.sequence, hl, 3, D), dtype=torch.bfloat16)
+                self.result = torch.zeros((1, world, splits[rank], hl, D), dtype=torch.bfloat16)
+                self.recv_buffer = type("Buffer", (), {"table": "receive-buffer table"})()
+
+            def barrier(self):
+                log.append("barrier")
+                dist.barrier()
+
+            def push(self, rows):
+                log.append("push")
+                assert rows.shape == (sp.sequence, hl, D) and rows.is_contiguous()
+                flat = rows.reshape(-1).view(torch.int16)
+                outgoing = [None] * world
+                for peer_rank, src_off, dst_off, nbytes in pkg.peer.push_plan(splits, rank, hl, D):
+                    assert dst_off == rank * splits[peer_rank] * hl * D * 2
+                    outgoing[peer_rank] = flat[src_off // 2:(src_off + nbytes) // 2].clone()
+                everything = [None] * world        # every rank's outgoing ranges (stands in for the peer stores)
+                dist.all_gather_object(everything, outgoing)
+                for src in range(world):
+                    self.result.view(torch.int16).view(world, -1)[src] = everything[src][rank]
+
+        def scatter(table, row0, sequence):
+            log.append("scatter")
+            assert table == "receive-buffer table" and row0 == sum(splits[:rank]) and sequence == seq
+            send = ref.pack_send(mine, world, 1)[0]                       # [world, L, hl, 3, D]
+            everything = [None] * world
+            dist.all_gather_object(everything, send)
+            start = 0
+            for src in range(world):
+                sp.peer.recv[0, start:start + splits[src]] = everything[src][rank]
+                start += splits[src]
+
+        def logged_attn(q, k, v):
+            log.append("attention")
+            return attn(q, k, v)
+
+        sp.peer = EmulatedPeer()
+        gathered = sp.attention_peer(scatter, logged_attn)
+        assert log == ["scatter", "barrier", "attention", "push", "barrier"], log
+        assert gathered is sp.peer.result
+        assert torch.equal(ref.unpack_gathered(gathered), want.reshape(splits[rank], heads * D))
+        assert torch.equal(gathered, sp.attention_packed(ref.pack_send(mine, world, 1), attn, overlap=False))
+        sp.peer = None
+        try:
+            sp.attention_peer(scatter, attn)
+            raise AssertionError("attention_peer without peer buffers must raise")
+        except RuntimeError as exc:
+            assert "enable_peer_exchange" in str(exc)
         Path(result_dir, f"r{rank}.txt").write_text("ok")
     finally:
         dist.destroy_process_group()
