@@ -213,7 +213,7 @@ def test_vae_temporal_chunk_decode_over_nccl(tmp_path, num_chunks):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    world = min(n, 4)
+    world = 2          # the reference's configuration (two ranks); larger worlds are covered on gloo
     mp.spawn(_vae_worker, args=(world, _free_port(), num_chunks, str(tmp_path)), nprocs=world, join=True)
     assert Path(tmp_path, "r0.txt").read_text() == "equal"
     for r in range(1, world):
